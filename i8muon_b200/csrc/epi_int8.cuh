@@ -1,0 +1,127 @@
+// Fused epilogues of the global-scale INT8 Newton-Schulz GEMMs (tcgen05 kind::i8,
+// int32 accumulation in tensor memory).
+//
+// Arithmetic restates the reference's INT8 GEMM modes (src/i8muon/csrc/int8.cu:254-352)
+// with every FP32 operation written un-fused so that a CPU restatement can
+// reproduce it bit for bit:
+//   I8_GRAM    G32 = A8 * A8^T  (lower tiles), gmax = max_{i != j} |G32_ij|   (int32, exact)
+//   I8_SQUARE  P_ij = g8_ij * (r_i + c_j) + (g8*g8)_ij * (gs*gs*c)
+//              r_i = (dG_i*c + b)*gs, c_j = (dG_j*gs)*c ;
+//              pmax = max |P_ij| over i != j, floor(i/128) >= floor(j/128)
+//   I8_UPDATE  Y_ij = (a8_ij * dP_i + (p8*a8)_ij * ps) * as ; non-final keeps FP32 + max,
+//              final casts to the user's dtype, un-pads, optionally transposes.
+#pragma once
+#include "epi_float.cuh"
+
+namespace i8m {
+
+enum I8Mode : int { I8_GRAM = 0, I8_SQUARE = 1, I8_UPDATE = 2, I8_UPDATE_FINAL = 3 };
+
+struct I8Args {
+  void* out;              // int32 (gram) / fp32 (square, update) (batch, m, n); final: user tensor
+  void* maximum;          // per-batch reduction slot: int32 (gram) or fp32 bits
+  const float* a_scale;   // per-batch scale of the left operand (square: gs, update: ps)
+  const float* b_scale;   // update: per-batch scale of A8 (as)
+  const float* diag;      // (batch, m): dG (square) or dP (update)
+  const int8_t* row_b;    // update: A8 (batch, m, n) row-major
+  float alpha, beta;      // square: b and c coefficients
+  int out_dtype, transpose;
+};
+
+template <int MODE>
+struct EpiI8 {
+  static constexpr int KIND = KIND_I8;
+  using Elem = int8_t;
+  static constexpr int PARTS = 1;
+  static constexpr bool BLOCKQ = false;
+  static constexpr int STAGES = 3;
+  static constexpr int MIN_CTAS = 2;
+  static constexpr uint32_t IDESC = make_idesc(2u, 1u, 1u, TILE, TILE);  // s32 <- s8 * s8
+  using Args = I8Args;
+
+  template <class Acc>
+  static __device__ __forceinline__ void run(const GemmGeom& g, const Args& a, const TileCtx& t,
+                                             const Acc& acc) {
+    const bool row_ok = t.row < g.m;
+    int imax = 0;
+    float fmax_ = 0.f;
+    float sa = 0.f, sb = 0.f, sq = 0.f, drow = 0.f, ri = 0.f;
+    if constexpr (MODE != I8_GRAM) {
+      sa = a.a_scale[t.b];
+      if (row_ok) drow = a.diag[size_t(t.b) * g.m + t.row];
+    }
+    if constexpr (MODE == I8_SQUARE) {
+      sq = __fmul_rn(__fmul_rn(sa, sa), a.beta);
+      ri = __fmul_rn(__fadd_rn(__fmul_rn(drow, a.beta), a.alpha), sa);
+    }
+    if constexpr (MODE == I8_UPDATE || MODE == I8_UPDATE_FINAL) sb = a.b_scale[t.b];
+#pragma unroll 1
+    for (int c = 0; c < TILE / 32; ++c) {
+      uint32_t v[32];
+      acc.load(c, v);
+      const int colb = t.col0 + c * 32;
+      if (colb >= g.n || !row_ok) continue;
+      const int ncol = min(32, g.n - colb);
+      const size_t rbase = (size_t(t.b) * g.m + t.row) * g.n + colb;
+      if constexpr (MODE == I8_GRAM) {
+        int iv[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          iv[j] = int(v[j]);
+          const int col = colb + j;
+          if (t.row < g.lm && col < g.ln && col != t.row) imax = max(imax, abs(iv[j]));
+        }
+        store_row<int>(static_cast<int*>(a.out) + rbase, iv, ncol);
+      } else {
+        float res[32];
+        // Row-major int8 companion of this row chunk (g8 for square, a8 for update).
+        const int8_t* comp = (MODE == I8_SQUARE)
+            ? static_cast<const int8_t*>(g.a_raw) + (size_t(t.b) * g.m + t.row) * g.k + colb
+            : a.row_b + rbase;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = colb + j;
+          float accf = float(int(v[j]));
+          float e = (col < g.n) ? float(comp[j]) : 0.f;
+          float r;
+          if constexpr (MODE == I8_SQUARE) {
+            float dcol = (col < g.n) ? a.diag[size_t(t.b) * g.m + col] : 0.f;
+            float cj = __fmul_rn(__fmul_rn(dcol, sa), a.beta);
+            r = __fadd_rn(__fmul_rn(e, __fadd_rn(ri, cj)), __fmul_rn(accf, sq));
+            if (col != t.row && (t.row >> 7) >= (col >> 7) && t.row < g.lm && col < g.ln)
+              fmax_ = fmaxf(fmax_, fabsf(r));
+          } else {
+            r = __fmul_rn(__fadd_rn(__fmul_rn(e, drow), __fmul_rn(accf, sa)), sb);
+            if (MODE == I8_UPDATE && t.row < g.lm && col < g.ln) fmax_ = fmaxf(fmax_, fabsf(r));
+          }
+          res[j] = r;
+        }
+        if constexpr (MODE == I8_UPDATE_FINAL) {
+          if (t.row < g.lm) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = colb + j;
+              if (col < g.ln) {
+                size_t idx = a.transpose ? (size_t(t.b) * g.ln + col) * g.lm + t.row
+                                         : (size_t(t.b) * g.lm + t.row) * g.ln + col;
+                store_user(a.out, a.out_dtype, idx, res[j]);
+              }
+            }
+          }
+        } else {
+          store_row<float>(static_cast<float*>(a.out) + rbase, res, ncol);
+        }
+      }
+    }
+    __syncwarp();
+    if constexpr (MODE == I8_GRAM) {
+      imax = warp_max_i(imax);
+      if (t.lane == 0 && imax > 0) atomicMax(static_cast<int*>(a.maximum) + t.b, imax);
+    } else if constexpr (MODE != I8_UPDATE_FINAL) {
+      fmax_ = warp_max(fmax_);
+      if (t.lane == 0 && fmax_ > 0.f) atomic_max_nonneg(static_cast<float*>(a.maximum) + t.b, fmax_);
+    }
+  }
+};
+
+}  // namespace i8m

@@ -1,0 +1,348 @@
+// Warp-specialised batched GEMM skeleton for sm_100a:  C[b] = A[b] * Bt[b]^T
+//
+//   A  is (batch, m, k) row-major  -> "K-major" operand tile of 128 rows
+//   Bt is (batch, n, k) row-major  -> rows of B^T, also K-major
+//
+// One CTA produces one 128 x 128 output tile.
+//   warp 0      TMA producer: cp.async.bulk.tensor 3-D boxes {128 bytes of K, 128 rows, 1 batch}
+//               with the 128-byte swizzle into a STAGES-deep shared-memory ring
+//   warp 1      allocates tensor memory and issues tcgen05.mma (one elected thread)
+//   warps 2..5  epilogue: tcgen05.ld the accumulator rows and run the fused epilogue
+//
+// Two accumulator disciplines:
+//   * whole-K accumulation (floating point and global-scale INT8): one 128-column
+//     accumulator, epilogue runs once after the last K block;
+//   * per-K-block promotion (128x128 block-quantised INT8 / E4M3): every 128-deep
+//     K block lands in a fresh accumulator (two TMEM buffers, ping-pong) and the
+//     epilogue warps fold it into FP32 registers with the block scales while the
+//     tensor core works on the next block.
+//
+// A debug core (geom.debug_simt) replaces TMA/tcgen05 by plain global-memory dot
+// products inside the epilogue threads, so that epilogue logic can be validated
+// independently of the tensor pipeline.  It is selected only by tests.
+#pragma once
+#include "ptx_sm100.cuh"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+namespace i8m {
+
+constexpr int TILE = 128;            // CTA tile is TILE x TILE
+constexpr int TILE_BYTES = TILE * 128;  // one operand tile of one stage (128 rows x 128 B)
+constexpr int GEMM_THREADS = 192;
+
+// Error codes written to the status word (first error wins).
+enum StatusCode : unsigned {
+  ST_OK = 0,
+  ST_PRODUCER_TIMEOUT = 0x100,
+  ST_MMA_TIMEOUT = 0x200,
+  ST_EPILOGUE_TIMEOUT = 0x300,
+};
+
+struct GemmGeom {
+  int batch;
+  int m, n, k;          // padded operand extents (elements)
+  int lm, ln;           // logical output extent
+  int tiles_m, tiles_n;
+  int sym;              // 1: only tiles with tm >= tn are computed
+  int tiles_per_batch;
+  int num_kb;           // K blocks of 128 bytes
+  int debug_simt;
+  const void* a_raw;    // raw operand pointers (debug core and epilogue reads)
+  const void* b_raw;
+  unsigned* status;
+};
+
+struct Ctrl {
+  unsigned long long full[8];
+  unsigned long long empty[8];
+  unsigned long long acc_full[2];
+  unsigned long long acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort;
+  float red[8];
+  int redi[8];
+};
+
+struct TileCtx {
+  int b, tm, tn, row0, col0;
+  int r;        // row inside the tile owned by this epilogue thread
+  int row;      // global row
+  int q;        // TMEM lane quarter of this warp
+  int lane;
+  Ctrl* ctrl;
+};
+
+__device__ __forceinline__ void decode_tile(const GemmGeom& g, int linear, int& b, int& tm,
+                                            int& tn) {
+  b = linear / g.tiles_per_batch;
+  int t = linear - b * g.tiles_per_batch;
+  if (g.sym) {
+    int i = int((sqrtf(float(8 * t + 1)) - 1.f) * 0.5f);
+    while ((i + 1) * (i + 2) / 2 <= t) ++i;
+    while (i * (i + 1) / 2 > t) --i;
+    tm = i;
+    tn = t - i * (i + 1) / 2;
+  } else {
+    tm = t / g.tiles_n;
+    tn = t - tm * g.tiles_n;
+  }
+}
+
+// ----------------------------------------------------- element conversions
+template <int KIND, typename Elem>
+struct ElemOps;
+template <>
+struct ElemOps<KIND_F16, __half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+};
+template <>
+struct ElemOps<KIND_F16, __nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+};
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(v, __NV_E4M3);
+  return __half2float(__half(h));
+}
+
+// Debug core: direct dot product over K range [k0, k1) of row `row` of A and
+// row `col` of Bt, returned as the raw 32-bit accumulator pattern.
+template <int KIND, typename Elem>
+__device__ inline uint32_t simt_dot(const GemmGeom& g, int b, int row, int col, int k0, int k1) {
+  if (row >= g.m || col >= g.n) return 0u;
+  const Elem* a = static_cast<const Elem*>(g.a_raw) + (size_t(b) * g.m + row) * g.k;
+  const Elem* bt = static_cast<const Elem*>(g.b_raw) + (size_t(b) * g.n + col) * g.k;
+  if (k1 > g.k) k1 = g.k;
+  if constexpr (KIND == KIND_I8) {
+    int acc = 0;
+    for (int kk = k0; kk < k1; ++kk) acc += int(a[kk]) * int(bt[kk]);
+    return uint32_t(acc);
+  } else if constexpr (KIND == KIND_F8) {
+    float acc = 0.f;
+    for (int kk = k0; kk < k1; ++kk)
+      acc = fmaf(e4m3_to_float(uint8_t(a[kk])), e4m3_to_float(uint8_t(bt[kk])), acc);
+    return __float_as_uint(acc);
+  } else if constexpr (KIND == KIND_TF32) {
+    float acc = 0.f;
+    for (int kk = k0; kk < k1; ++kk) acc = fmaf(float(a[kk]), float(bt[kk]), acc);
+    return __float_as_uint(acc);
+  } else {
+    float acc = 0.f;
+    for (int kk = k0; kk < k1; ++kk) acc = fmaf(float(a[kk]), float(bt[kk]), acc);
+    return __float_as_uint(acc);
+  }
+}
+
+// ------------------------------------------------------------ accumulators
+// Whole-K accumulator: chunk c = columns [32c, 32c+32) of this thread's row.
+template <int KIND, typename Elem>
+struct AccWholeK {
+  const GemmGeom& g;
+  const TileCtx& t;
+  uint32_t taddr;  // TMEM address of (lane quarter base, column 0)
+  __device__ __forceinline__ void load(int c, uint32_t (&v)[32]) const {
+    if (g.debug_simt) {
+#pragma unroll 1
+      for (int j = 0; j < 32; ++j)
+        v[j] = simt_dot<KIND, Elem>(g, t.b, t.row, t.col0 + c * 32 + j, 0, g.k);
+    } else {
+      __syncwarp();  // tcgen05.ld is warp-collective: reconverge after masked stores
+      tmem_ld32(taddr + uint32_t(c * 32), v);
+      tmem_wait_ld();
+    }
+  }
+};
+
+// ------------------------------------------------------------------ kernel
+// Epi supplies:
+//   KIND, Elem, PARTS (operand planes per side: 1, or 2 for split-TF32),
+//   BLOCKQ (per-K-block promotion), STAGES, MIN_CTAS, IDESC, struct Args,
+//   static __device__ void run(g, args, t, acc)              (whole-K)
+//   static __device__ void run_blockq(g, args, t, tmem, ctrl) (per-K-block)
+template <class Epi>
+__global__ void __launch_bounds__(GEMM_THREADS, Epi::MIN_CTAS)
+ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
+               GemmGeom g, typename Epi::Args args) {
+  constexpr int STAGES = Epi::STAGES;
+  constexpr int PARTS = Epi::PARTS;
+  constexpr int STAGE_BYTES = 2 * PARTS * TILE_BYTES;
+  constexpr int TMEM_COLS = Epi::BLOCKQ ? 256 : 128;
+  constexpr int BKE = 128 / int(sizeof(typename Epi::Elem));  // elements per 128-byte K block
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  int b, tm, tn;
+  decode_tile(g, blockIdx.x, b, tm, tn);
+  const int row0 = tm * TILE, col0 = tn * TILE;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&ctrl->acc_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->acc_empty[i]), 128);
+    }
+    ctrl->abort = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+  volatile uint32_t* abort_flag = &ctrl->abort;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (!g.debug_simt && warp == 0 && lane == 0) {
+    // ------------------------------------------------------------ producer
+    int issued = 0;
+    bool ok = true;
+    for (int kb = 0; kb < g.num_kb; ++kb) {
+      const int s = kb % STAGES;
+      if (kb >= STAGES) {
+        ok = mbar_wait(smem_u32(&ctrl->empty[s]), uint32_t((kb / STAGES) - 1) & 1u, abort_flag);
+        if (!ok) break;
+      }
+      const uint32_t bar = smem_u32(&ctrl->full[s]);
+      const uint32_t dst = smem_base + uint32_t(s * STAGE_BYTES);
+      mbar_arrive_expect_tx(bar, STAGE_BYTES);
+      tma_load_3d(dst, &map_a, bar, kb * BKE, row0, b);
+      tma_load_3d(dst + PARTS * TILE_BYTES, &map_b, bar, kb * BKE, col0, b);
+      if constexpr (PARTS == 2) {
+        tma_load_3d(dst + TILE_BYTES, &map_a2, bar, kb * BKE, row0, b);
+        tma_load_3d(dst + 3 * TILE_BYTES, &map_b2, bar, kb * BKE, col0, b);
+      }
+      issued = kb + 1;
+    }
+    if (!ok) {
+      atomicCAS(g.status, 0u, unsigned(ST_PRODUCER_TIMEOUT) | unsigned(blockIdx.x & 0xff));
+      // Let the copies that were issued land before shared memory is released.
+      int first = issued > STAGES ? issued - STAGES : 0;
+      for (int kb = first; kb < issued; ++kb) {
+        uint32_t bar = smem_u32(&ctrl->full[kb % STAGES]);
+        uint32_t parity = uint32_t(kb / STAGES) & 1u;
+        for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(bar, parity); ++spin) {
+        }
+      }
+    }
+  } else if (!g.debug_simt && warp == 1 && lane == 0) {
+    // ---------------------------------------------------------- MMA issuer
+    bool ok = true;
+    for (int kb = 0; kb < g.num_kb; ++kb) {
+      const int s = kb % STAGES;
+      ok = mbar_wait(smem_u32(&ctrl->full[s]), uint32_t(kb / STAGES) & 1u, abort_flag);
+      if (!ok) break;
+      uint32_t d = tmem_base;
+      if constexpr (Epi::BLOCKQ) {
+        const int buf = kb & 1;
+        if (kb >= 2) {
+          ok = mbar_wait(smem_u32(&ctrl->acc_empty[buf]), uint32_t((kb >> 1) - 1) & 1u, abort_flag);
+          if (!ok) break;
+        }
+        d = tmem_base + uint32_t(buf * TILE);
+      }
+      tc_fence_after();
+      const uint32_t sa = smem_base + uint32_t(s * STAGE_BYTES);
+      const uint32_t sb = sa + PARTS * TILE_BYTES;
+      const uint64_t adesc = make_smem_desc_sw128(sa);
+      const uint64_t bdesc = make_smem_desc_sw128(sb);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        // 32 bytes of K per instruction: advance the start address inside the
+        // 128-byte swizzle row (address field is in 16-byte units).
+        const uint64_t adv = uint64_t(ks * 2);
+        uint32_t accumulate = Epi::BLOCKQ ? (ks > 0) : (kb > 0 || ks > 0);
+        umma<Epi::KIND>(d, adesc + adv, bdesc + adv, Epi::IDESC, accumulate);
+        if constexpr (PARTS == 2) {
+          // split-TF32: hi*hi (above) + hi*lo + lo*hi
+          const uint64_t a2 = make_smem_desc_sw128(sa + TILE_BYTES) + adv;
+          const uint64_t b2 = make_smem_desc_sw128(sb + TILE_BYTES) + adv;
+          umma<Epi::KIND>(d, adesc + adv, b2, Epi::IDESC, 1u);
+          umma<Epi::KIND>(d, a2, bdesc + adv, Epi::IDESC, 1u);
+        }
+      }
+      umma_commit(smem_u32(&ctrl->empty[s]));
+      if constexpr (Epi::BLOCKQ) umma_commit(smem_u32(&ctrl->acc_full[kb & 1]));
+    }
+    if constexpr (!Epi::BLOCKQ) {
+      if (ok) umma_commit(smem_u32(&ctrl->acc_full[0]));
+    }
+    if (!ok) atomicCAS(g.status, 0u, unsigned(ST_MMA_TIMEOUT) | unsigned(blockIdx.x & 0xff));
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------ epilogue
+    TileCtx t;
+    t.b = b; t.tm = tm; t.tn = tn; t.row0 = row0; t.col0 = col0;
+    t.q = warp & 3; t.lane = lane;
+    t.r = t.q * 32 + lane;
+    t.row = row0 + t.r;
+    t.ctrl = ctrl;
+    const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16);
+    if constexpr (Epi::BLOCKQ) {
+      Epi::run_blockq(g, args, t, taddr, abort_flag);
+    } else {
+      bool ok = true;
+      if (!g.debug_simt) {
+        ok = mbar_wait(smem_u32(&ctrl->acc_full[0]), 0u, abort_flag);
+        tc_fence_after();
+      }
+      if (ok) {
+        AccWholeK<Epi::KIND, typename Epi::Elem> acc{g, t, taddr};
+        Epi::run(g, args, t, acc);
+      } else if (lane == 0) {
+        atomicCAS(g.status, 0u, unsigned(ST_EPILOGUE_TIMEOUT) | unsigned(blockIdx.x & 0xff));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ------------------------------------------------------------ store helpers
+// Store `count` (<= 32) consecutive elements; vectorised when the destination
+// is 16-byte aligned and the chunk is complete.
+template <typename T>
+__device__ __forceinline__ void store_row(T* dst, const T (&vals)[32], int count) {
+  if (count == 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+    constexpr int VEC = 16 / int(sizeof(T));
+    const uint4* src = reinterpret_cast<const uint4*>(vals);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 32 / VEC; ++i) d4[i] = src[i];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < count) dst[j] = vals[j];
+  }
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ int warp_max_i(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Finite non-negative floats order like their bit patterns.
+__device__ __forceinline__ void atomic_max_nonneg(float* p, float v) {
+  atomicMax(reinterpret_cast<int*>(p), __float_as_int(v));
+}
+
+}  // namespace i8m

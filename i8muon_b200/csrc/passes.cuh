@@ -1,0 +1,441 @@
+// Memory-bound passes around the Newton-Schulz GEMMs: input statistics
+// (Frobenius norm + abs-max in one read), normalise / quantise prologues with a
+// fused transpose, the symmetric and output re-quantisers of the global-scale
+// INT8 path, and the two fused optimizer kernels (momentum, decay + update).
+//
+// All of them are HBM-bound: one coalesced read of the input, one coalesced
+// write of each output, 32x32 or 128x128 shared-memory tiles for the transposed
+// copies.  FP32 expressions are written un-fused (the library is also compiled
+// with --fmad=false) so that the CPU restatement reproduces them bit for bit.
+#pragma once
+#include "epi_bq.cuh"
+
+namespace i8m {
+
+template <typename T>
+__device__ __forceinline__ float load_f(const T* p, size_t i) { return widen<T>(p[i]); }
+
+__device__ __forceinline__ int8_t quant_rn(float x, float multiplier) {
+  return int8_t(max(-127, min(127, __float2int_rn(__fmul_rn(x, multiplier)))));
+}
+
+// ------------------------------------------------------------------ stats
+// Pass 1: each block reduces STATS_CHUNK elements of one matrix to a partial
+// sum of squares and a partial abs-max.  Pass 2: one block per matrix folds the
+// partials in a fixed order (deterministic) into norm[b] = sqrt(sum), amax[b].
+// Restates src/i8muon/csrc/int8.cu:41-62 plus the torch Frobenius norm of
+// src/i8muon/_cutlass.py:190 as one read of the input.
+constexpr int STATS_THREADS = 256;
+constexpr int STATS_CHUNK = STATS_THREADS * 32;
+
+__device__ __forceinline__ float block_sum_256(float v, float* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+  if (threadIdx.x < 32) {
+    r = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  }
+  __syncthreads();
+  return r;  // valid in warp 0
+}
+__device__ __forceinline__ float block_max_256(float v, float* sh) {
+  v = warp_max(v);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+  if (threadIdx.x < 32) {
+    r = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.f;
+    r = warp_max(r);
+  }
+  __syncthreads();
+  return r;
+}
+
+template <typename In>
+__global__ void __launch_bounds__(STATS_THREADS)
+stats_partial_kernel(const In* x, float* partial_sum, float* partial_max, long long count,
+                     int chunks) {
+  __shared__ float sh[8];
+  const int b = blockIdx.y, chunk = blockIdx.x;
+  const In* src = x + size_t(b) * count;
+  long long base = (long long)chunk * STATS_CHUNK;
+  float s = 0.f, mx = 0.f;
+#pragma unroll 8
+  for (int i = 0; i < 32; ++i) {
+    long long idx = base + threadIdx.x + i * STATS_THREADS;
+    float v = idx < count ? load_f(src, size_t(idx)) : 0.f;
+    s = __fmaf_rn(v, v, s);
+    mx = fmaxf(mx, fabsf(v));
+  }
+  s = block_sum_256(s, sh);
+  mx = block_max_256(mx, sh);
+  if (threadIdx.x == 0) {
+    partial_sum[size_t(b) * chunks + chunk] = s;
+    partial_max[size_t(b) * chunks + chunk] = mx;
+  }
+}
+
+__global__ void __launch_bounds__(STATS_THREADS)
+stats_final_kernel(const float* partial_sum, const float* partial_max, float* norm, float* amax,
+                   int chunks) {
+  __shared__ float sh[8];
+  const int b = blockIdx.x;
+  float s = 0.f, mx = 0.f;
+  for (int i = threadIdx.x; i < chunks; i += STATS_THREADS) {
+    s += partial_sum[size_t(b) * chunks + i];
+    mx = fmaxf(mx, partial_max[size_t(b) * chunks + i]);
+  }
+  s = block_sum_256(s, sh);
+  mx = block_max_256(mx, sh);
+  if (threadIdx.x == 0) {
+    if (norm) norm[b] = sqrtf(s);
+    if (amax) amax[b] = mx;
+  }
+}
+
+// -------------------------------------------------------------- normalise
+// A = E(x * inv), A^T, zero padded to (m x n); restates src/i8muon/csrc/prec.cu:46-68.
+// For E = float the value is split into two TF32-representable planes.
+template <typename In, typename E>
+__global__ void __launch_bounds__(256)
+normalize_kernel(const In* x, const float* norm, E* out, E* out_t, float* out_lo, float* out_t_lo,
+                 int rows, int cols, int m, int n, int transpose, float eps) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z;
+  const float nb = norm ? norm[b] : 1.f;
+  const float inv = nb == 0.f ? 0.f : 1.f / fmaxf(nb, eps);
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  // Tiles are taken in the INPUT's orientation so that reads are coalesced.
+  // Without transpose A = x; with transpose A^T has the input's orientation.
+  const int prow = transpose ? n : m, pcol = transpose ? m : n;
+  E* primary = transpose ? out_t : out;
+  float* primary_lo = transpose ? out_t_lo : out_lo;
+  E* secondary = transpose ? out : out_t;
+  float* secondary_lo = transpose ? out_lo : out_t_lo;
+  auto put = [](E* dst, float* dst_lo, size_t o, float v) {
+    if constexpr (sizeof(E) == 4) {
+      const float hi = tf32_hi(v);
+      dst[o] = hi;
+      dst_lo[o] = v - hi;
+    } else {
+      dst[o] = round_to<E>(v);
+    }
+  };
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int r = ty + j;
+    const int row = blockIdx.y * 32 + r, col = blockIdx.x * 32 + tx;
+    float v = 0.f;
+    if (row < rows && col < cols) v = __fmul_rn(load_f(x, (size_t(b) * rows + row) * cols + col), inv);
+    tile[r][tx] = v;
+    if (primary != nullptr && row < prow && col < pcol) put(primary, primary_lo, (size_t(b) * prow + row) * pcol + col, v);
+  }
+  __syncthreads();
+  if (secondary == nullptr) return;
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int r = ty + j;
+    const int row = blockIdx.x * 32 + r, col = blockIdx.y * 32 + tx;
+    if (row < pcol && col < prow) put(secondary, secondary_lo, (size_t(b) * pcol + row) * prow + col, tile[tx][r]);
+  }
+}
+
+// ------------------------------------------------------------ input quant
+// Global-scale INT8 quantisation of the input (round half to even), its
+// transpose, and a_scale[b] = amax / (127 * max(norm, eps)); restates
+// src/i8muon/csrc/int8.cu:64-100.  use_norm == 0 means norm = 1 and eps = 0.
+template <typename In>
+__global__ void __launch_bounds__(256)
+input_quant_kernel(const In* x, const float* amax, const float* norm, int8_t* out, int8_t* out_t,
+                   float* scale, int rows, int cols, int m, int n, int transpose, float eps) {
+  __shared__ int8_t tile[32][33];
+  const int b = blockIdx.z;
+  const float mx = amax[b];
+  const float nb = norm ? norm[b] : 1.f;
+  const float multiplier = mx > 0.f ? 127.f / mx : 0.f;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+    scale[b] = mx > 0.f ? mx / __fmul_rn(127.f, fmaxf(nb, eps)) : 0.f;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  // Tile origin in the INPUT: rows blockIdx.y*32, cols blockIdx.x*32.
+  // Without transpose A = x (m x n padded); with transpose A^T has the input's
+  // layout (n x m padded) and A is written through the shared tile.
+  const int prow = transpose ? n : m, pcol = transpose ? m : n;
+  int8_t* primary = transpose ? out_t : out;
+  int8_t* secondary = transpose ? out : out_t;
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int r = ty + j;
+    const int row = blockIdx.y * 32 + r, col = blockIdx.x * 32 + tx;
+    int8_t q = 0;
+    if (row < rows && col < cols) q = quant_rn(load_f(x, (size_t(b) * rows + row) * cols + col), multiplier);
+    tile[r][tx] = q;
+    if (row < prow && col < pcol) primary[(size_t(b) * prow + row) * pcol + col] = q;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int r = ty + j;
+    const int row = blockIdx.x * 32 + r, col = blockIdx.y * 32 + tx;
+    if (row < pcol && col < prow) secondary[(size_t(b) * pcol + row) * prow + col] = tile[tx][r];
+  }
+}
+
+// -------------------------------------------------------- symmetric quant
+// Reads the lower-triangular 32x32 tiles of the int32 Gram (QUAD = false) or of
+// the FP32 polynomial (QUAD = true), quantises with the global scale and a
+// zeroed diagonal, mirrors to a full symmetric int8 matrix, and writes the FP32
+// diagonal and the new scale; restates src/i8muon/csrc/int8.cu:363-420.
+template <typename In, bool QUAD>
+__global__ void __launch_bounds__(256)
+symmetric_quant_kernel(const In* input, const void* maximum, const float* orig_scale,
+                       const float* orig_diag, int8_t* output, float* scale, float* diag, int m,
+                       float c0, float c1, float c2) {
+  __shared__ int8_t tile[32][33];
+  const int b = blockIdx.y, pid = blockIdx.x;
+  int tm = int((sqrtf(float(8 * pid + 1)) - 1.f) * 0.5f);
+  while ((tm + 1) * (tm + 2) / 2 <= pid) ++tm;
+  while (tm * (tm + 1) / 2 > pid) --tm;
+  const int tn = pid - tm * (tm + 1) / 2;
+  float mx;
+  if constexpr (QUAD) mx = static_cast<const float*>(maximum)[b];
+  else mx = float(static_cast<const int*>(maximum)[b]);
+  const float multiplier = mx > 0.f ? 127.f / mx : 0.f;
+  const float os = orig_scale[b];
+  const float sa = QUAD ? 1.f : __fmul_rn(os, os);
+  if (pid == 0 && threadIdx.x == 0) scale[b] = mx > 0.f ? sa / multiplier : 0.f;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int r = ty + j;
+    const int row = tm * 32 + r, col = tn * 32 + tx;
+    float v = (row < m && col < m) ? float(input[(size_t(b) * m + row) * m + col]) : 0.f;
+    int8_t q = (row == col) ? int8_t(0) : quant_rn(v, multiplier);
+    if (row == col && row < m) {
+      if constexpr (QUAD) {
+        const float d = orig_diag[size_t(b) * m + row];
+        diag[size_t(b) * m + row] =
+            __fadd_rn(__fadd_rn(v, __fmul_rn(__fadd_rn(__fmul_rn(c2, d), c1), d)), c0);
+      } else {
+        diag[size_t(b) * m + row] = __fmul_rn(v, sa);
+      }
+    }
+    tile[r][tx] = q;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int r = ty + j;
+    int row = tm * 32 + r, col = tn * 32 + tx;
+    if (row < m && col < m) {
+      // a diagonal tile takes its upper half from the mirrored lower half
+      int8_t q = (tm == tn && r < tx) ? tile[tx][r] : tile[r][tx];
+      output[(size_t(b) * m + row) * m + col] = q;
+    }
+    if (tm != tn) {
+      row = tn * 32 + r; col = tm * 32 + tx;
+      if (row < m && col < m) output[(size_t(b) * m + row) * m + col] = tile[tx][r];
+    }
+  }
+}
+
+// ----------------------------------------------------------- output quant
+// FP32 (m x n) -> int8 and transposed int8 with the global scale 1/(127/max);
+// restates src/i8muon/csrc/int8.cu:422-450.
+__global__ void __launch_bounds__(256)
+output_quant_kernel(const float* input, const float* maximum, int8_t* out, int8_t* out_t,
+                    float* scale, int m, int n) {
+  __shared__ int8_t tile[32][33];
+  const int b = blockIdx.z;
+  const float mx = maximum[b];
+  const float multiplier = mx > 0.f ? 127.f / mx : 0.f;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+    scale[b] = mx > 0.f ? 1.f / multiplier : 0.f;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int r = ty + j;
+    const int row = blockIdx.y * 32 + r, col = blockIdx.x * 32 + tx;
+    int8_t q = 0;
+    if (row < m && col < n) {
+      q = quant_rn(input[(size_t(b) * m + row) * n + col], multiplier);
+      out[(size_t(b) * m + row) * n + col] = q;
+    }
+    tile[r][tx] = q;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int r = ty + j;
+    const int row = blockIdx.x * 32 + r, col = blockIdx.y * 32 + tx;
+    if (row < n && col < m) out_t[(size_t(b) * n + row) * m + col] = tile[tx][r];
+  }
+}
+
+// --------------------------------------------------------------- BQ quant
+// Per-128x128-block quantisation of x * inv: block max (floor 1e-8) -> scale,
+// INT8 truncating or E4M3 round-to-nearest-even saturating; writes A, A^T and
+// the scale grid; restates src/i8muon/csrc/bq.cu:60-101.
+// A 128x128 block is processed as sixteen 32x32 sub-tiles by 256 threads.
+template <typename In, bool FP8>
+__global__ void __launch_bounds__(256)
+bq_quant_kernel(const In* x, const float* norm, uint8_t* out, uint8_t* out_t, float* scale,
+                int rows, int cols, int m, int n, int transpose, float eps) {
+  __shared__ float sh[8];
+  __shared__ uint8_t qt[128][132];
+  const int tmb = blockIdx.x, tnb = blockIdx.y, b = blockIdx.z;
+  const float nb = norm ? norm[b] : 1.f;
+  float inv = 1.f / fmaxf(nb, eps);
+  if (nb == 0.f) inv = 0.f;
+  // Thread layout chosen for coalesced INPUT reads: without transpose the block
+  // rows are input rows; with transpose the block rows are input columns.
+  float vals[64];
+  float mx = 1e-8f;
+  const int tx = threadIdx.x & 127, ty = threadIdx.x >> 7;  // 128 x 2
+#pragma unroll
+  for (int i = 0; i < 64; ++i) {
+    // element (p, tx) of the 128x128 patch in INPUT orientation
+    const int p = ty + 2 * i;
+    int ir, ic;
+    if (!transpose) { ir = tmb * 128 + p; ic = tnb * 128 + tx; }
+    else { ir = tnb * 128 + p; ic = tmb * 128 + tx; }
+    float v = (ir < rows && ic < cols) ? __fmul_rn(load_f(x, (size_t(b) * rows + ir) * cols + ic), inv) : 0.f;
+    vals[i] = v;
+    mx = fmaxf(mx, fabsf(v));
+  }
+  mx = block_max_256(mx, sh);
+  __shared__ float s_mult;
+  if (threadIdx.x == 0) {
+    const float multiplier = (FP8 ? 448.f : 127.f) / mx;
+    s_mult = multiplier;
+    scale[(size_t(b) * (m / 128) + tmb) * (n / 128) + tnb] = 1.f / multiplier;
+  }
+  __syncthreads();
+  const float multiplier = s_mult;
+  // The matrix that shares the input's orientation is written directly.
+  uint8_t* same = transpose ? out_t : out;     // rows = input rows
+  uint8_t* other = transpose ? out : out_t;
+  const int srow0 = transpose ? tnb * 128 : tmb * 128, scol0 = transpose ? tmb * 128 : tnb * 128;
+  const int sld = transpose ? m : n;
+  const int srows = transpose ? n : m;
+#pragma unroll
+  for (int i = 0; i < 64; ++i) {
+    const int p = ty + 2 * i;
+    uint8_t q = bq_quant<FP8>(vals[i], multiplier);
+    qt[p][tx] = q;
+    same[(size_t(b) * srows + srow0 + p) * sld + scol0 + tx] = q;
+  }
+  __syncthreads();
+  const int old = transpose ? n : m;
+  const int orows = transpose ? m : n;
+#pragma unroll
+  for (int i = 0; i < 64; ++i) {
+    const int p = ty + 2 * i;  // row of the transposed patch
+    other[(size_t(b) * orows + scol0 + p) * old + srow0 + tx] = qt[tx][p];
+  }
+}
+
+// ----------------------------------------------------- optimizer kernels
+// Up to MT_MAX same-shaped tensors per launch; pointers travel as kernel
+// arguments so that no device-side pointer table (and no host-to-device copy)
+// is needed and the launch can be captured in a CUDA graph.
+constexpr int MT_MAX = 32;
+struct MomentumTable {
+  const void* grad[MT_MAX];
+  void* buf[MT_MAX];
+};
+struct ApplyTable {
+  void* param[MT_MAX];
+};
+
+__device__ __forceinline__ float lerp_f(float start, float end, float w) {
+  // torch.lerp: two-sided formula selected by |w| < 0.5
+  const float d = end - start;
+  return fabsf(w) < 0.5f ? __fmaf_rn(w, d, start) : __fmaf_rn(-d, 1.f - w, end);
+}
+
+// buf <- lerp(buf, g, 1 - mu2) (rounded to the buffer's dtype), then
+// u = nesterov ? lerp(g, buf, mu) : buf, written to the stacked update tensor
+// (count x numel) in the gradient's dtype; restates src/i8muon/_optimizer.py:472-474.
+template <typename T>
+__global__ void __launch_bounds__(256)
+momentum_kernel(MomentumTable tab, T* update, long long numel, float w_buf, float mu,
+                int nesterov) {
+  const int t = blockIdx.y;
+  const T* g = static_cast<const T*>(tab.grad[t]);
+  T* buf = static_cast<T*>(tab.buf[t]);
+  T* u = update + size_t(t) * numel;
+  constexpr int VEC = 16 / int(sizeof(T));
+  const long long nvec = numel / VEC;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(buf) |
+                         reinterpret_cast<uintptr_t>(u)) & 15u) == 0;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (aligned) {
+    for (; i < nvec; i += stride) {
+      uint4 gv = reinterpret_cast<const uint4*>(g)[i];
+      uint4 bv = reinterpret_cast<uint4*>(buf)[i];
+      uint4 uv;
+      const T* ge = reinterpret_cast<const T*>(&gv);
+      T* be = reinterpret_cast<T*>(&bv);
+      T* ue = reinterpret_cast<T*>(&uv);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float gf = widen<T>(ge[e]);
+        const T nb = round_to<T>(lerp_f(widen<T>(be[e]), gf, w_buf));
+        be[e] = nb;
+        ue[e] = nesterov ? round_to<T>(lerp_f(gf, widen<T>(nb), mu)) : nb;
+      }
+      reinterpret_cast<uint4*>(buf)[i] = bv;
+      reinterpret_cast<uint4*>(u)[i] = uv;
+    }
+    i = nvec * VEC + (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  }
+  for (; i < numel; i += stride) {
+    const float gf = widen<T>(g[i]);
+    const T nb = round_to<T>(lerp_f(widen<T>(buf[i]), gf, w_buf));
+    buf[i] = nb;
+    u[i] = nesterov ? round_to<T>(lerp_f(gf, widen<T>(nb), mu)) : nb;
+  }
+}
+
+// decay_mode 0: none; 1: param *= decay (then rounded) ; 2: update += wd * param
+// (rounded to the update dtype).  Then param += (-lr) * update.  Restates
+// src/i8muon/_optimizer.py:503-511 including its intermediate roundings.
+template <typename P, typename U>
+__global__ void __launch_bounds__(256)
+apply_kernel(ApplyTable tab, const U* update, long long numel, int decay_mode, float decay,
+             float neg_lr) {
+  const int t = blockIdx.y;
+  P* p = static_cast<P*>(tab.param[t]);
+  const U* u = update + size_t(t) * numel;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  constexpr int VEC = 8;
+  const long long nvec = numel / VEC;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(p) % (VEC * sizeof(P))) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(u) % (VEC * sizeof(U))) == 0);
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  auto one = [&](float pf, float uf) -> float {
+    if (decay_mode == 1) pf = widen<P>(round_to<P>(__fmul_rn(pf, decay)));
+    else if (decay_mode == 2) uf = widen<U>(round_to<U>(__fmaf_rn(decay, pf, uf)));
+    return __fmaf_rn(neg_lr, uf, pf);
+  };
+  if (aligned) {
+    struct alignas(VEC * sizeof(P)) PV { P e[VEC]; };
+    struct alignas(VEC * sizeof(U)) UV { U e[VEC]; };
+    for (; i < nvec; i += stride) {
+      PV pv = reinterpret_cast<PV*>(p)[i];
+      const UV uv = reinterpret_cast<const UV*>(u)[i];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) pv.e[e] = round_to<P>(one(widen<P>(pv.e[e]), widen<U>(uv.e[e])));
+      reinterpret_cast<PV*>(p)[i] = pv;
+    }
+    i = nvec * VEC + (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  }
+  for (; i < numel; i += stride) p[i] = round_to<P>(one(widen<P>(p[i]), widen<U>(u[i])));
+}
+
+}  // namespace i8m

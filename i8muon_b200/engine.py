@@ -1,0 +1,139 @@
+"""Newton-Schulz engine: the object the optimizer routes every matrix through.
+
+Drop-in for the reference's ``CutlassNSInt8`` (src/i8muon/_cutlass.py:15-49):
+same constructor arguments, the same four entry points ``_regular_prec``,
+``_gram_prec``, ``_regular_i8`` and ``_regular_bq`` with the call convention
+``fn(x, coeffs=None, eps=1e-7, deterministic=True, precision=...) -> Tensor``
+(same shape and dtype as ``x``; leading dimensions fold into the batch), and the
+same ``router``.  Each entry point is one call into the sm_100a library
+(``i8m_ns_run``), which sequences the fused kernels on the current stream.
+
+Differences that a caller can observe:
+  * only compute capability 10.x devices are accepted;
+  * ``deterministic`` is accepted and ignored - the norm reduction is always the
+    deterministic two-pass one;
+  * the result is a fresh tensor, not a view into the call's workspace;
+  * ``tiles`` is validated and recorded but the kernels use one 128x128 CTA tile.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from functools import lru_cache
+
+import torch
+
+from . import native
+from .coefficients import DEFAULT_COEFFICIENTS
+from .routing import matrix_spec, normalize_precision, select_route
+
+_COMPUTE_CODES = {"float32": native.F32, "float16": native.F16, "bfloat16": native.BF16}
+_STATUS_WORDS = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """One zeroed int32 per device that kernels write an error code to when a
+    bounded device-side wait gives up."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _STATUS_WORDS.get(index)
+    if word is None:
+        word = _STATUS_WORDS[index] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
+    return word
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any kernel on ``device`` reported a timed-out wait."""
+    devices = list(_STATUS_WORDS) if device is None else [torch.device(device).index or 0]
+    for index in devices:
+        word = _STATUS_WORDS.get(index)
+        if word is None:
+            continue
+        code = int(word.item())
+        if code:
+            word.zero_()
+            raise native.NativeError(f"device-side wait timed out, status word 0x{code:x}")
+
+
+def _coefficient_array(coeffs):
+    rows = [tuple(float(v) for v in row) for row in coeffs]
+    if not rows or any(len(row) != 3 for row in rows):
+        raise ValueError("Expected a nonempty list of (a, b, c) coefficients")
+    flat = [v for row in rows for v in row]
+    return (ctypes.c_double * len(flat))(*flat), len(rows)
+
+
+class CutlassNSInt8:
+    """Native floating-point regular/Gram NS and regular INT8 / INT8-BQ / FP8-BQ NS."""
+
+    def __init__(self, autotune=False, *, tiles=None, fp16_first=True):
+        self.fp16_first = fp16_first
+        self.autotune = autotune
+        self.tiles = dict(tiles or {})
+        if (set(self.tiles) - {"aat", "square", "update"}
+                or any(v not in (0, 1, 2, 3, 4) for v in self.tiles.values())):
+            raise ValueError("tiles accepts aat/square/update with values 0/1/2/3/4")
+        self._routes = {}
+
+    # ------------------------------------------------------------ routing
+    def router(self, M: int, N: int, precision: str, use_gram: bool, gram_aspect_threshold: float):
+        key = (M, N, precision, use_gram, gram_aspect_threshold)
+        hit = self._routes.get(key)
+        if hit is None:
+            name, compute = select_route(M, N, precision, use_gram, gram_aspect_threshold)
+            hit = self._routes[key] = (getattr(self, name), compute)
+        return hit
+
+    # ------------------------------------------------------------- launch
+    def _run(self, route, x, coeffs, eps, compute, alignment, spec_precision, fp16_first):
+        coeffs = DEFAULT_COEFFICIENTS if coeffs is None else coeffs
+        shape = x.shape
+        batch, rows, cols, *_ = matrix_spec(tuple(shape), x.dtype, x.device, spec_precision, alignment)
+        x = x.contiguous()
+        dtype = native.torch_dtype_code(x.dtype)
+        array, steps = _coefficient_array(coeffs)
+        order = os.environ.get("I8MUON_GRAM_RESET", "00100") if route == native.ROUTE_GRAM else None
+        if order is not None and (not order or order[0] != "0" or set(order) - {"0", "1"}):
+            raise ValueError("I8MUON_GRAM_RESET must be a binary string starting with 0")
+        with torch.cuda.device(x.device):
+            size = native.ns_workspace_bytes(route, batch, rows, cols, dtype, compute, steps, fp16_first)
+            workspace = torch.empty(size, dtype=torch.uint8, device=x.device)
+            out = torch.empty_like(x)
+            native.call("i8m_ns_run", route, x.data_ptr(), out.data_ptr(), dtype, batch, rows, cols,
+                        compute, array, steps, float(eps), int(bool(fp16_first)),
+                        order.encode() if order is not None else None, workspace.data_ptr(), size,
+                        status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        # The workspace may be reused by later allocations on this stream only.
+        return out.view(shape)
+
+    def _regular_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16"):
+        """FP32 / BF16 / FP16 regular NS (src/i8muon/_cutlass_prec.py:90-106)."""
+        precision = normalize_precision(precision)
+        if precision not in _COMPUTE_CODES:
+            raise ValueError(f"Unsupported floating-point precision: {precision}")
+        return self._run(native.ROUTE_FLOAT, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False)
+
+    def _gram_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16"):
+        """Gram-space NS with restarts given by I8MUON_GRAM_RESET (src/i8muon/_cutlass_prec.py:107-130)."""
+        precision = normalize_precision(precision)
+        if precision not in _COMPUTE_CODES:
+            raise ValueError(f"Unsupported floating-point precision: {precision}")
+        return self._run(native.ROUTE_GRAM, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False)
+
+    def _regular_i8(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="int8", *, block=False):
+        """Global-scale INT8 NS, optionally after one FP16 iteration (src/i8muon/_cutlass.py:130-142)."""
+        if block:
+            return self._run(native.ROUTE_BQ_INT8, x, coeffs, eps, native.F16, 128, "int8", self.fp16_first)
+        return self._run(native.ROUTE_INT8, x, coeffs, eps, native.F16, 16, "int8", self.fp16_first)
+
+    def _regular_bq(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float8_e4m3fn"):
+        """128x128 block-quantised NS: INT8 honours fp16_first, E4M3 never does
+        (src/i8muon/_cutlass.py:71-76)."""
+        precision = normalize_precision(precision)
+        if precision in ("int8_bq", "int8"):
+            return self._regular_i8(x, coeffs, eps, deterministic, "int8", block=True)
+        if precision != "float8_e4m3fn":
+            raise ValueError(f"Unsupported block-quantised precision: {precision}")
+        return self._run(native.ROUTE_BQ_FP8, x, coeffs, eps, native.F16, 128, precision, False)
+
+
+__all__ = ["CutlassNSInt8", "check_status", "status_word"]

@@ -1,0 +1,371 @@
+"""Muon optimizer and the functional ``muon_step``.
+
+Same public surface and update rule as the reference (src/i8muon/_optimizer.py:
+``Muon`` 168-408, ``muon_step`` 416-511).  What differs is how the step runs on
+the device:
+
+  * parameters with the same (device, dtypes, shape) form a group and go through
+    Newton-Schulz as ONE batched call, instead of one call per parameter;
+  * the momentum blend (both lerps) is one multi-tensor kernel that writes the
+    stacked update tensor directly, and weight decay + the learning-rate-scaled
+    update is one multi-tensor kernel; their roundings match the eager torch
+    sequence of the reference;
+  * with ``use_cuda_graph`` the momentum kernel and the whole Newton-Schulz call
+    of a group are captured together and replayed; the apply kernel stays
+    outside the graph so that learning-rate schedules keep working.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+from torch import Tensor
+from torch.optim.optimizer import Optimizer, ParamsT
+
+from . import native
+from .coefficients import recommend_coefficients
+from .engine import CutlassNSInt8
+from .routing import (EPS, GRAM_ASPECT_THRESHOLD, adjust_lr, matrix_spec, normalize_precision,
+                      validate_ns_device)
+
+__all__ = ["Muon", "muon_step"]
+
+# Largest stacked update (bytes) that one Newton-Schulz call may take; larger
+# groups are processed in several batched calls to bound the workspace.
+MAX_GROUP_BYTES = int(os.environ.get("I8MUON_B200_MAX_GROUP_BYTES", str(2 << 30)))
+
+
+def _check_group(group) -> None:
+    lr = group["lr"]
+    if isinstance(lr, Tensor) and lr.numel() != 1:
+        raise ValueError("Tensor lr must be 1-element")
+    for name in ("weight_decay", "eps"):
+        if not 0.0 <= group[name]:
+            raise ValueError(f"{name} must be >= 0")
+    coeffs = group["ns_coefficients"]
+    if coeffs is not None and (not coeffs or any(len(row) != 3 for row in coeffs)):
+        raise ValueError("Expected a nonempty list of (a, b, c) coefficients")
+    momentum = group["momentum"]
+    if isinstance(momentum, (int, float)):
+        momentum = (momentum,)
+    if len(momentum) not in (1, 2) or any(not 0.0 <= m for m in momentum):
+        raise ValueError("momentum must contain one or two nonnegative values")
+    group["momentum"] = tuple(momentum)
+    adjust = group["adjust_lr_fn"]
+    if adjust is not None and not callable(adjust) and adjust not in (
+            "spectral", "original", "match_rms_adamw", "none"):
+        raise ValueError(f"adjust_lr_fn {adjust} is not supported")
+    group["precision"] = normalize_precision(group["precision"])
+    if group["weight_decay_mode"] not in ("absolute", "base_lr", "adjusted_lr"):
+        raise ValueError("weight_decay_mode must be 'absolute', 'base_lr' or 'adjusted_lr'")
+
+
+def _graph_key(ns_fn, layout, count, precision, coefficients, eps, deterministic, engine, momentum,
+               pointers):
+    """One graph owns the addresses and constants of one group's momentum + NS."""
+    schedule = recommend_coefficients() if coefficients is None else coefficients
+    return (engine, ns_fn.__name__, layout.device, layout.dtype, tuple(layout.shape), count, precision,
+            tuple(tuple(row) for row in schedule), eps, deterministic, engine.fp16_first,
+            tuple(sorted(engine.tiles.items())), os.environ.get("I8MUON_GRAM_RESET", "00100"),
+            momentum, pointers)
+
+
+class Muon(Optimizer):
+    """Muon: momentum updates orthogonalised by Newton-Schulz on B200 tensor cores.
+
+    Matrix parameters (two or more dimensions; leading dimensions are batches)
+    use Newton-Schulz; scalar and vector parameters can be handed to
+    ``scalar_optimizer``, which is stepped after the Muon groups.  A scalar
+    ``momentum`` keeps one moving average; ``(mu, mu2)`` blends Nesterov-style
+    with buffer decay ``mu2``.
+
+    ``precision``: auto, int8, int8_bq, fp8, float16, bfloat16 or float32.  Both
+    INT8 routes run their first iteration in FP16 when ``fp16_first`` is true.
+    ``use_gram`` allows the Gram-space iteration for matrices whose aspect ratio
+    reaches ``gram_aspect_threshold``.  ``ns_coefficients`` gives one (a, b, c)
+    row per iteration; otherwise ``ns_steps`` (default 5) selects the INT8-safety
+    schedule.  ``adjust_lr_fn``: "spectral", "original", "match_rms_adamw",
+    "none"/None, or a callable (lr, rows, cols).  ``weight_decay_mode``:
+    "base_lr" (default), "adjusted_lr" or "absolute".
+    """
+
+    def __init__(
+        self,
+        params: ParamsT,
+        lr: float = 0.01,
+        weight_decay: float = 0.0,
+        momentum=(0.95, 0.95),
+        ns_coefficients=None,
+        ns_steps: Optional[int] = None,
+        eps: float = EPS,
+        adjust_lr_fn="spectral",
+        *,
+        weight_decay_mode: str = "base_lr",
+        precision: str = "auto",
+        autotune: bool = False,
+        fp16_first: bool = True,
+        use_gram: bool = True,
+        use_cuda_graph: bool = False,
+        gram_aspect_threshold: float = GRAM_ASPECT_THRESHOLD,
+        deterministic: bool = True,
+        scalar_optimizer: Optional[Optimizer] = None,
+    ) -> None:
+        precision = normalize_precision(precision)
+        if ns_coefficients is None:
+            ns_coefficients = recommend_coefficients(iters=5 if ns_steps is None else ns_steps)
+        self._ns = CutlassNSInt8(autotune=autotune, fp16_first=fp16_first)
+        self._use_cuda_graph = use_cuda_graph
+        self._ns_graphs: dict = {}
+        self._gram_aspect_threshold = gram_aspect_threshold
+        self.scalar_optimizer = None  # attached once the Muon groups exist
+        defaults = dict(lr=lr, weight_decay=weight_decay, weight_decay_mode=weight_decay_mode,
+                        momentum=momentum, ns_coefficients=ns_coefficients, eps=eps,
+                        adjust_lr_fn=adjust_lr_fn, deterministic=deterministic, use_gram=use_gram,
+                        precision=precision)
+        super().__init__(params, defaults)
+        self._require_disjoint(scalar_optimizer, self._all_matrix_ids())
+        self.scalar_optimizer = scalar_optimizer
+
+    # ---------------------------------------------------------- validation
+    def _all_matrix_ids(self):
+        return {id(p) for group in self._muon_param_groups for p in group["params"]}
+
+    @staticmethod
+    def _require_disjoint(scalar, matrix_ids):
+        if scalar is None:
+            return
+        if any(id(p) in matrix_ids for group in scalar.param_groups for p in group["params"]):
+            raise ValueError("Muon and scalar_optimizer must have disjoint parameters")
+
+    def _validate_param_group(self, group):
+        _check_group(group)
+        for p in group["params"]:
+            if p.ndim < 2 or min(p.shape[-2:]) < 1 or not p.is_floating_point():
+                raise ValueError("Muon only supports nonempty real floating >=2D parameters")
+            if p.is_cuda:
+                method, compute = self._ns.router(*p.shape[-2:], group["precision"], group["use_gram"],
+                                                  self._gram_aspect_threshold)
+                matrix_spec(tuple(p.shape), p.dtype, p.device, compute,
+                            128 if method.__name__ == "_regular_bq" else 16)
+
+    def add_param_group(self, param_group):
+        group = dict(param_group)
+        params = group["params"]
+        if isinstance(params, Tensor):
+            params = [params]
+        if isinstance(params, set):
+            raise TypeError("Optimizer parameters must have a deterministic order")
+        group["params"] = list(params)
+        merged = dict(self.defaults, **group)
+        self._validate_param_group(merged)
+        scalar = self.scalar_optimizer
+        self._require_disjoint(scalar, {id(p) for p in group["params"]})
+        self.scalar_optimizer = None
+        try:
+            super().add_param_group(merged)
+        finally:
+            self.scalar_optimizer = scalar
+
+    # -------------------------------------------- param_groups / state dict
+    @property
+    def param_groups(self):
+        """Muon groups followed by the scalar optimizer's, so that learning-rate
+        schedulers see both."""
+        if self.scalar_optimizer is None:
+            return self._muon_param_groups
+        return self._muon_param_groups + self.scalar_optimizer.param_groups
+
+    @param_groups.setter
+    def param_groups(self, value):
+        self._muon_param_groups = value
+
+    def __setstate__(self, state):
+        state = dict(state)
+        if "param_groups" in state:
+            state["_muon_param_groups"] = state.pop("param_groups")
+        super().__setstate__(state)
+        for group in self._muon_param_groups:
+            # checkpoints written before weight_decay_mode existed decayed with the adjusted rate
+            group.setdefault("weight_decay_mode", "adjusted_lr")
+
+    def _without_scalar(self, fn, *args):
+        scalar, self.scalar_optimizer = self.scalar_optimizer, None
+        try:
+            return fn(*args)
+        finally:
+            self.scalar_optimizer = scalar
+
+    def state_dict(self):
+        """Muon state only; the scalar optimizer keeps its own state dict."""
+        return self._without_scalar(super().state_dict)
+
+    def load_state_dict(self, state_dict):
+        def load():
+            Optimizer.load_state_dict(self, state_dict)
+            self._ns_graphs.clear()
+        return self._without_scalar(load)
+
+    # ---------------------------------------------------------------- step
+    def step(self, closure=None):
+        with torch.no_grad():
+            loss = None
+            if closure is not None:
+                with torch.enable_grad():
+                    loss = closure()
+            for group in self._muon_param_groups:
+                params, grads, bufs = [], [], []
+                for p in group["params"]:
+                    if p.grad is None:
+                        continue
+                    state = self.state[p]
+                    buf = state.get("momentum_buffer")
+                    if buf is None:
+                        buf = state["momentum_buffer"] = torch.zeros_like(
+                            p.grad, memory_format=torch.preserve_format)
+                    params.append(p)
+                    grads.append(p.grad)
+                    bufs.append(buf)
+                muon_step(params, grads, bufs, lr=group["lr"], weight_decay=group["weight_decay"],
+                          weight_decay_mode=group["weight_decay_mode"], momentum=group["momentum"],
+                          ns_coefficients=group["ns_coefficients"], eps=group["eps"],
+                          adjust_lr_fn=group["adjust_lr_fn"], deterministic=group["deterministic"],
+                          ns_engine=self._ns, precision=group["precision"], use_gram=group["use_gram"],
+                          use_cuda_graph=self._use_cuda_graph, ns_graphs=self._ns_graphs,
+                          gram_aspect_threshold=self._gram_aspect_threshold)
+            if self.scalar_optimizer is not None:
+                self.scalar_optimizer.step()
+            return loss
+
+
+def _as_float(value) -> float:
+    return float(value.item()) if isinstance(value, Tensor) else float(value)
+
+
+def _momentum_and_ns(grads, bufs, update, ns_fn, ns_kwargs, w_buf, mu, nesterov):
+    stream = torch.cuda.current_stream().cuda_stream
+    native.call("i8m_momentum", native.pointer_array([g.data_ptr() for g in grads]),
+                native.pointer_array([b.data_ptr() for b in bufs]), len(grads), update.data_ptr(),
+                grads[0].numel(), native.torch_dtype_code(update.dtype), w_buf, mu, int(nesterov), stream)
+    return ns_fn(update, **ns_kwargs)
+
+
+def muon_step(
+    params,
+    grads,
+    momentum_bufs,
+    *,
+    lr,
+    weight_decay,
+    momentum,
+    ns_coefficients,
+    eps,
+    adjust_lr_fn,
+    deterministic: bool = True,
+    ns_engine: CutlassNSInt8,
+    precision: str = "auto",
+    use_gram: bool = True,
+    use_cuda_graph: bool = False,
+    ns_graphs: Optional[dict] = None,
+    gram_aspect_threshold: float = GRAM_ASPECT_THRESHOLD,
+    weight_decay_mode: str = "base_lr",
+) -> None:
+    """Apply one Muon update in place to ``params`` and ``momentum_bufs``.
+
+    For every parameter: buf <- lerp(buf, grad, 1 - mu2); update = lerp(grad, buf, mu)
+    (Nesterov, two momentum values) or buf; update <- NewtonSchulz(update); decoupled
+    weight decay; param <- param - adjusted_lr * update.
+    """
+    if ns_graphs is None:
+        ns_graphs = {}
+    if not params:
+        return
+    lr = _as_float(lr)
+    weight_decay = float(weight_decay)
+    if weight_decay_mode not in ("absolute", "base_lr", "adjusted_lr"):
+        raise ValueError("weight_decay_mode must be 'absolute', 'base_lr' or 'adjusted_lr'")
+    momentum = tuple(momentum) if not isinstance(momentum, (int, float)) else (momentum,)
+    nesterov = len(momentum) == 2
+    mu, mu2 = float(momentum[0]), float(momentum[-1])
+    precision = normalize_precision(precision)
+
+    # group parameters that can share one batched Newton-Schulz call
+    groups: dict = {}
+    for index, param in enumerate(params):
+        grad, buf = grads[index], momentum_bufs[index]
+        if grad.shape != param.shape or buf.shape != grad.shape or buf.dtype != grad.dtype:
+            raise ValueError("parameter, gradient and momentum buffer must agree in shape; "
+                             "gradient and buffer in dtype")
+        key = (grad.device, grad.dtype, param.dtype, tuple(grad.shape))
+        groups.setdefault(key, []).append(index)
+
+    for (device, gdtype, pdtype, shape), members in groups.items():
+        M, N = shape[-2], shape[-1]
+        ns_fn, actual = ns_engine.router(M, N, precision, use_gram, gram_aspect_threshold)
+        validate_ns_device(device, actual)
+        native.torch_dtype_code(gdtype)
+        adjusted = adjust_lr(lr, adjust_lr_fn, shape)
+        ns_kwargs = dict(coeffs=ns_coefficients, eps=eps, deterministic=deterministic, precision=actual)
+        per_tensor = 1
+        for d in shape:
+            per_tensor *= d
+        leading = per_tensor // (M * N)
+        chunk = max(1, min(len(members), MAX_GROUP_BYTES // max(1, per_tensor * grads[members[0]].element_size()),
+                           65535 // max(1, leading)))
+        with torch.cuda.device(device):
+            for first in range(0, len(members), chunk):
+                part = members[first:first + chunk]
+                g_list = [grads[i] if grads[i].is_contiguous() else grads[i].contiguous() for i in part]
+                b_list, p_list, copy_back = [], [], []
+                for i in part:
+                    b, p = momentum_bufs[i], params[i]
+                    if not b.is_contiguous():
+                        c = b.contiguous(); copy_back.append((b, c)); b = c
+                    if not p.is_contiguous():
+                        c = p.contiguous(); copy_back.append((p, c)); p = c
+                    b_list.append(b); p_list.append(p)
+                count = len(part)
+                if use_cuda_graph and not copy_back:
+                    pointers = tuple(t.data_ptr() for t in g_list + b_list)
+                    key = _graph_key(ns_fn, g_list[0], count, actual, ns_coefficients, eps, deterministic,
+                                     ns_engine, (mu, mu2, nesterov), pointers)
+                    captured = ns_graphs.get(key)
+                    if captured is None:
+                        update = torch.empty((count, *shape), device=device, dtype=gdtype)
+                        # Warm up outside capture on copies so the real buffers are not advanced.
+                        scratch_b = [b.clone() for b in b_list]
+                        for _ in range(2):
+                            _momentum_and_ns(g_list, scratch_b, update, ns_fn, ns_kwargs, 1.0 - mu2, mu, nesterov)
+                        del scratch_b
+                        torch.cuda.current_stream().synchronize()
+                        graph = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(graph):
+                            ortho = _momentum_and_ns(g_list, b_list, update, ns_fn, ns_kwargs,
+                                                     1.0 - mu2, mu, nesterov)
+                        # keep the tensors whose addresses the graph holds alive
+                        captured = ns_graphs[key] = (graph, update, ortho, g_list, b_list)
+                    else:
+                        pass
+                    captured[0].replay()
+                    ortho = captured[2]
+                else:
+                    update = torch.empty((count, *shape), device=device, dtype=gdtype)
+                    ortho = _momentum_and_ns(g_list, b_list, update, ns_fn, ns_kwargs, 1.0 - mu2, mu, nesterov)
+
+                if callable(adjust_lr_fn):
+                    adjusted = adjust_lr(lr, adjust_lr_fn, shape)
+                adjusted = _as_float(adjusted)
+                if weight_decay == 0:
+                    mode, decay = 0, 0.0
+                elif weight_decay_mode == "adjusted_lr":
+                    mode, decay = 2, weight_decay
+                elif weight_decay_mode == "absolute":
+                    mode, decay = 1, 1.0 - weight_decay
+                else:
+                    mode, decay = 1, 1.0 - lr * weight_decay
+                native.call("i8m_apply", native.pointer_array([p.data_ptr() for p in p_list]), count,
+                            ortho.data_ptr(), per_tensor, native.torch_dtype_code(pdtype),
+                            native.torch_dtype_code(gdtype), mode, decay, -adjusted,
+                            torch.cuda.current_stream().cuda_stream)
+                for original, contiguous in copy_back:
+                    original.copy_(contiguous)
