@@ -54,6 +54,7 @@ struct EpiBq {
   using Elem = uint8_t;
   static constexpr int PARTS = 1;
   static constexpr bool BLOCKQ = true;
+  static constexpr int PROMOTE_KB = 1;
   static constexpr int STAGES = 4;
   static constexpr int MIN_CTAS = 1;
   static constexpr uint32_t IDESC =
@@ -75,6 +76,7 @@ struct EpiBq {
       const int buf = kb & 1;
       if (!g.debug_simt) {
         ok = mbar_wait(smem_u32(&t.ctrl->acc_full[buf]), uint32_t(kb >> 1) & 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);  // keep the warp together for tcgen05.ld
         if (!ok) break;
         tc_fence_after();
       }

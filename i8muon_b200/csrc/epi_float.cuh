@@ -50,9 +50,23 @@ __device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) {
 template <>
 __device__ __forceinline__ float widen<float>(float v) { return v; }
 
-// FP32 values travel between GEMMs as two TF32-representable planes.
+// FP32 values travel between GEMMs as two planes: hi = v rounded to the nearest
+// TF32 value (ties to even), lo = v - hi exactly.  Rounding instead of truncating
+// keeps |lo| <= 2^-11 |v| with no sign bias, so the dropped lo*lo term of the
+// three-product expansion stays near 2^-24 relative.
 __device__ __forceinline__ float tf32_hi(float v) {
-  return __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+  uint32_t u = __float_as_uint(v);
+  u += 0xfffu + ((u >> 13) & 1u);
+  return __uint_as_float(u & 0xffffe000u);
+}
+// Low plane of the split.  The tensor core reads only the upper 19 bits of an
+// operand, so the remainder is rounded (not truncated) to that width here.
+__device__ __forceinline__ float tf32_lo(float v, float hi) {
+#ifdef I8M_TF32_EXACT_LO
+  return v - hi;
+#else
+  return tf32_hi(v - hi);
+#endif
 }
 
 __device__ __forceinline__ void store_user(void* out, int dtype, size_t index, float v) {
@@ -68,7 +82,12 @@ struct EpiFloat {
   using Elem = E;
   static constexpr int PARTS = IS_F32 ? 2 : 1;
   static constexpr bool BLOCKQ = false;
-  static constexpr int STAGES = IS_F32 ? 3 : 3;
+  // FP32: fold the TMEM accumulator into registers after every K block (32 elements of
+  // K, 12 tensor-core accumulations).  The tensor core accumulates with truncation:
+  // measured bias of a whole-K Gram diagonal is about -1e-8 * K relative, which at
+  // K = 4096 alone would exceed the 1e-5 bar of this path.
+  static constexpr int PROMOTE_KB = IS_F32 ? 1 : 0;
+  static constexpr int STAGES = 3;
   static constexpr int MIN_CTAS = IS_F32 ? 1 : 2;
   static constexpr uint32_t FMT = IS_F32 ? 2u : (std::is_same<E, __nv_bfloat16>::value ? 1u : 0u);
   static constexpr uint32_t IDESC = make_idesc(1u, FMT, FMT, TILE, TILE);
@@ -80,12 +99,11 @@ struct EpiFloat {
     const bool row_ok = t.row < g.m;
     const bool diag_tile = g.sym && t.tm == t.tn;
     const bool mirror = g.sym && t.tm != t.tn;
-#pragma unroll 1
-    for (int c = 0; c < TILE / 32; ++c) {
+    auto body = [&](const int c) {
       uint32_t v[32];
       acc.load(c, v);
       const int colb = t.col0 + c * 32;
-      if (colb >= g.n) continue;  // uniform per CTA
+      if (colb >= g.n) return;  // uniform per CTA
       float val[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
@@ -104,7 +122,7 @@ struct EpiFloat {
         // Values outside the logical extent are stored as zero padding.
         val[j] = (t.row < g.lm && col < g.ln) ? widen<E>(round_to<E>(x)) : 0.f;
       }
-      if (!row_ok) continue;
+      if (!row_ok) return;
       const int ncol = min(32, g.n - colb);
       if constexpr (MODE == MODE_FINAL) {
         if (t.row < g.lm) {
@@ -126,7 +144,7 @@ struct EpiFloat {
           if constexpr (IS_F32) {
             float hi[32], lo[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) { hi[j] = tf32_hi(val[j]); lo[j] = val[j] - hi[j]; }
+            for (int j = 0; j < 32; ++j) { hi[j] = tf32_hi(val[j]); lo[j] = tf32_lo(val[j], hi[j]); }
             store_row<float>(reinterpret_cast<float*>(out) + rbase, hi, ncol);
             store_row<float>(out_lo + rbase, lo, ncol);
           } else {
@@ -151,8 +169,9 @@ struct EpiFloat {
             size_t d1 = (size_t(t.b) * g.m + col) * g.n + t.row;
             if constexpr (IS_F32) {
               float hi = tf32_hi(val[j]);
-              reinterpret_cast<float*>(out)[d0] = hi; out_lo[d0] = val[j] - hi;
-              reinterpret_cast<float*>(out)[d1] = hi; out_lo[d1] = val[j] - hi;
+              const float lo = tf32_lo(val[j], hi);
+              reinterpret_cast<float*>(out)[d0] = hi; out_lo[d0] = lo;
+              reinterpret_cast<float*>(out)[d1] = hi; out_lo[d1] = lo;
             } else {
               out[d0] = round_to<E>(val[j]);
               out[d1] = round_to<E>(val[j]);
@@ -161,13 +180,20 @@ struct EpiFloat {
             size_t d1 = (size_t(t.b) * (mirror ? g.m : g.n) + col) * tld + t.row;
             if constexpr (IS_F32) {
               float hi = tf32_hi(val[j]);
-              reinterpret_cast<float*>(tdst)[d1] = hi; tdst_lo[d1] = val[j] - hi;
+              reinterpret_cast<float*>(tdst)[d1] = hi; tdst_lo[d1] = tf32_lo(val[j], hi);
             } else {
               tdst[d1] = round_to<E>(val[j]);
             }
           }
         }
       }
+    };
+    if constexpr (Acc::IN_REGS) {
+#pragma unroll
+      for (int c = 0; c < TILE / 32; ++c) body(c);
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < TILE / 32; ++c) body(c);
     }
   }
 };

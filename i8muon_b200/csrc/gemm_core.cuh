@@ -117,7 +117,7 @@ __device__ inline uint32_t simt_dot(const GemmGeom& g, int b, int row, int col, 
   if (k1 > g.k) k1 = g.k;
   if constexpr (KIND == KIND_I8) {
     int acc = 0;
-    for (int kk = k0; kk < k1; ++kk) acc += int(a[kk]) * int(bt[kk]);
+    for (int kk = k0; kk < k1; ++kk) acc += int(int8_t(a[kk])) * int(int8_t(bt[kk]));
     return uint32_t(acc);
   } else if constexpr (KIND == KIND_F8) {
     float acc = 0.f;
@@ -139,6 +139,7 @@ __device__ inline uint32_t simt_dot(const GemmGeom& g, int b, int row, int col, 
 // Whole-K accumulator: chunk c = columns [32c, 32c+32) of this thread's row.
 template <int KIND, typename Elem>
 struct AccWholeK {
+  static constexpr bool IN_REGS = false;
   const GemmGeom& g;
   const TileCtx& t;
   uint32_t taddr;  // TMEM address of (lane quarter base, column 0)
@@ -155,10 +156,24 @@ struct AccWholeK {
   }
 };
 
+// Accumulator already folded into registers (chunked promotion): same chunk
+// interface, compile-time indexing so that the array stays in registers.
+struct AccRegs {
+  static constexpr bool IN_REGS = true;
+  const float (&total)[TILE];
+  __device__ __forceinline__ void load(int c, uint32_t (&v)[32]) const {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(total[c * 32 + j]);
+  }
+};
+
 // ------------------------------------------------------------------ kernel
 // Epi supplies:
 //   KIND, Elem, PARTS (operand planes per side: 1, or 2 for split-TF32),
-//   BLOCKQ (per-K-block promotion), STAGES, MIN_CTAS, IDESC, struct Args,
+//   PROMOTE_KB (0: the whole K extent accumulates in tensor memory; n > 0: every n
+//   K blocks the partial accumulator is folded into FP32 registers by the epilogue
+//   warps while the tensor core fills the other TMEM buffer), BLOCKQ (the fold is
+//   the block-scaled promotion of run_blockq), STAGES, MIN_CTAS, IDESC, struct Args,
 //   static __device__ void run(g, args, t, acc)              (whole-K)
 //   static __device__ void run_blockq(g, args, t, tmem, ctrl) (per-K-block)
 template <class Epi>
@@ -169,7 +184,8 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr int STAGES = Epi::STAGES;
   constexpr int PARTS = Epi::PARTS;
   constexpr int STAGE_BYTES = 2 * PARTS * TILE_BYTES;
-  constexpr int TMEM_COLS = Epi::BLOCKQ ? 256 : 128;
+  constexpr int PROMOTE = Epi::PROMOTE_KB;
+  constexpr int TMEM_COLS = PROMOTE > 0 ? 256 : 128;
   constexpr int BKE = 128 / int(sizeof(typename Epi::Elem));  // elements per 128-byte K block
 
   extern __shared__ uint8_t smem_raw[];
@@ -247,10 +263,15 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       ok = mbar_wait(smem_u32(&ctrl->full[s]), uint32_t(kb / STAGES) & 1u, abort_flag);
       if (!ok) break;
       uint32_t d = tmem_base;
-      if constexpr (Epi::BLOCKQ) {
-        const int buf = kb & 1;
-        if (kb >= 2) {
-          ok = mbar_wait(smem_u32(&ctrl->acc_empty[buf]), uint32_t((kb >> 1) - 1) & 1u, abort_flag);
+      bool chunk_first = kb == 0, chunk_last = false;
+      int buf = 0;
+      if constexpr (PROMOTE > 0) {
+        const int chunk = kb / PROMOTE;
+        buf = chunk & 1;
+        chunk_first = (kb % PROMOTE) == 0;
+        chunk_last = (kb % PROMOTE) == PROMOTE - 1 || kb == g.num_kb - 1;
+        if (chunk_first && chunk >= 2) {
+          ok = mbar_wait(smem_u32(&ctrl->acc_empty[buf]), uint32_t((chunk >> 1) - 1) & 1u, abort_flag);
           if (!ok) break;
         }
         d = tmem_base + uint32_t(buf * TILE);
@@ -265,7 +286,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // 32 bytes of K per instruction: advance the start address inside the
         // 128-byte swizzle row (address field is in 16-byte units).
         const uint64_t adv = uint64_t(ks * 2);
-        uint32_t accumulate = Epi::BLOCKQ ? (ks > 0) : (kb > 0 || ks > 0);
+        uint32_t accumulate = (chunk_first && ks == 0) ? 0u : 1u;
         umma<Epi::KIND>(d, adesc + adv, bdesc + adv, Epi::IDESC, accumulate);
         if constexpr (PARTS == 2) {
           // split-TF32: hi*hi (above) + hi*lo + lo*hi
@@ -273,12 +294,17 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint64_t b2 = make_smem_desc_sw128(sb + TILE_BYTES) + adv;
           umma<Epi::KIND>(d, adesc + adv, b2, Epi::IDESC, 1u);
           umma<Epi::KIND>(d, a2, bdesc + adv, Epi::IDESC, 1u);
+#ifdef I8M_TF32_LOLO
+          umma<Epi::KIND>(d, a2, b2, Epi::IDESC, 1u);
+#endif
         }
       }
       umma_commit(smem_u32(&ctrl->empty[s]));
-      if constexpr (Epi::BLOCKQ) umma_commit(smem_u32(&ctrl->acc_full[kb & 1]));
+      if constexpr (PROMOTE > 0) {
+        if (chunk_last) umma_commit(smem_u32(&ctrl->acc_full[buf]));
+      }
     }
-    if constexpr (!Epi::BLOCKQ) {
+    if constexpr (PROMOTE == 0) {
       if (ok) umma_commit(smem_u32(&ctrl->acc_full[0]));
     }
     if (!ok) atomicCAS(g.status, 0u, unsigned(ST_MMA_TIMEOUT) | unsigned(blockIdx.x & 0xff));
@@ -293,10 +319,49 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16);
     if constexpr (Epi::BLOCKQ) {
       Epi::run_blockq(g, args, t, taddr, abort_flag);
+    } else if constexpr (PROMOTE > 0) {
+      if (g.debug_simt) {
+        AccWholeK<Epi::KIND, typename Epi::Elem> acc{g, t, taddr};
+        Epi::run(g, args, t, acc);
+      } else {
+        // Chunked promotion: the tensor core accumulates with truncation, so a
+        // long K extent is folded into registers (round-to-nearest adds) every
+        // PROMOTE K blocks.
+        float total[TILE];
+#pragma unroll
+        for (int j = 0; j < TILE; ++j) total[j] = 0.f;
+        const int chunks = (g.num_kb + PROMOTE - 1) / PROMOTE;
+        bool ok = true;
+#pragma unroll 1
+        for (int c = 0; c < chunks; ++c) {
+          const int buf = c & 1;
+          ok = mbar_wait(smem_u32(&ctrl->acc_full[buf]), uint32_t(c >> 1) & 1u, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int cc = 0; cc < TILE / 32; ++cc) {
+            uint32_t v[32];
+            tmem_ld32(taddr + uint32_t(buf * TILE + cc * 32), v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) total[cc * 32 + j] = __fadd_rn(total[cc * 32 + j], __uint_as_float(v[j]));
+          }
+          tc_fence_before();
+          mbar_arrive(smem_u32(&ctrl->acc_empty[buf]));
+        }
+        if (ok) {
+          AccRegs acc{total};
+          Epi::run(g, args, t, acc);
+        } else if (lane == 0) {
+          atomicCAS(g.status, 0u, unsigned(ST_EPILOGUE_TIMEOUT) | unsigned(blockIdx.x & 0xff));
+        }
+      }
     } else {
       bool ok = true;
       if (!g.debug_simt) {
         ok = mbar_wait(smem_u32(&ctrl->acc_full[0]), 0u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);  // keep the warp together for tcgen05.ld
         tc_fence_after();
       }
       if (ok) {

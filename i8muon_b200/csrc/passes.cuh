@@ -120,7 +120,7 @@ normalize_kernel(const In* x, const float* norm, E* out, E* out_t, float* out_lo
     if constexpr (sizeof(E) == 4) {
       const float hi = tf32_hi(v);
       dst[o] = hi;
-      dst_lo[o] = v - hi;
+      dst_lo[o] = tf32_lo(v, hi);
     } else {
       dst[o] = round_to<E>(v);
     }

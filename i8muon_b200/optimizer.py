@@ -29,7 +29,7 @@ from .engine import CutlassNSInt8
 from .routing import (EPS, GRAM_ASPECT_THRESHOLD, adjust_lr, matrix_spec, normalize_precision,
                       validate_ns_device)
 
-__all__ = ["Muon", "muon_step"]
+__all__ = ["Muon", "muon_step", "native_step_ops"]
 
 # Largest stacked update (bytes) that one Newton-Schulz call may take; larger
 # groups are processed in several batched calls to bound the workspace.
@@ -369,3 +369,45 @@ def muon_step(
                             torch.cuda.current_stream().cuda_stream)
                 for original, contiguous in copy_back:
                     original.copy_(contiguous)
+
+
+def native_step_ops(ns_engine: CutlassNSInt8, *, lr, weight_decay, momentum, ns_coefficients, eps=EPS,
+                    adjust_lr_fn="spectral", precision="auto", use_gram=True,
+                    gram_aspect_threshold=GRAM_ASPECT_THRESHOLD, weight_decay_mode="base_lr"):
+    """The three device operations of one step as callables over stacked same-shape
+    matrices, for ``sharding.ShardedMuonStep``: fused momentum kernel, one batched
+    Newton-Schulz call, fused decay + update kernel."""
+    from .sharding import StepOps
+    lr = _as_float(lr)
+    momentum = tuple(momentum) if not isinstance(momentum, (int, float)) else (momentum,)
+    nesterov = len(momentum) == 2
+    mu, mu2 = float(momentum[0]), float(momentum[-1])
+    precision = normalize_precision(precision)
+
+    def do_momentum(grads, bufs, out):
+        native.call("i8m_momentum", native.pointer_array([g.data_ptr() for g in grads]),
+                    native.pointer_array([b.data_ptr() for b in bufs]), len(grads), out.data_ptr(),
+                    grads[0].numel(), native.torch_dtype_code(out.dtype), 1.0 - mu2, mu, int(nesterov),
+                    torch.cuda.current_stream().cuda_stream)
+
+    def do_ns(x):
+        fn, actual = ns_engine.router(x.shape[-2], x.shape[-1], precision, use_gram, gram_aspect_threshold)
+        return fn(x, coeffs=ns_coefficients, eps=eps, deterministic=True, precision=actual)
+
+    def do_apply(params, updates):
+        shape = params[0].shape
+        adjusted = _as_float(adjust_lr(lr, adjust_lr_fn, shape))
+        if weight_decay == 0:
+            mode, decay = 0, 0.0
+        elif weight_decay_mode == "adjusted_lr":
+            mode, decay = 2, weight_decay
+        elif weight_decay_mode == "absolute":
+            mode, decay = 1, 1.0 - weight_decay
+        else:
+            mode, decay = 1, 1.0 - lr * weight_decay
+        native.call("i8m_apply", native.pointer_array([p.data_ptr() for p in params]), len(params),
+                    updates.data_ptr(), params[0].numel(), native.torch_dtype_code(params[0].dtype),
+                    native.torch_dtype_code(updates.dtype), mode, decay, -adjusted,
+                    torch.cuda.current_stream().cuda_stream)
+
+    return StepOps(momentum=do_momentum, orthogonalise=do_ns, apply=do_apply)

@@ -1,0 +1,161 @@
+"""Multi-GPU Muon step: parameter matrices are partitioned across ranks by their
+Newton-Schulz cost, each rank orthogonalises its own share, and the updates are
+exchanged with one all-gather per shape group.
+
+The reference is single-device (it contains no collective at all); this module
+is the one place where the step shards naturally, because every matrix is an
+independent unit.  Every rank holds all parameters and all gradients (data-
+parallel training), keeps the momentum buffers of the matrices it owns, and
+after the all-gather applies weight decay and the scaled update to every
+parameter locally, so parameters stay replicated without a broadcast.
+
+Only local memory is read by kernels: the collective (NCCL over NVLink, or gloo
+in CPU tests) lands remote updates in this rank's own buffer first.
+
+The arithmetic is injected through ``StepOps`` so that the partition and gather
+bookkeeping can be exercised on CPU ranks with stand-in operations.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def ns_flops(shape: Sequence[int], steps: int) -> float:
+    """Algorithmic cost of regular Newton-Schulz: steps * (4 l^2 h + 2 l^3) per matrix
+    (Gram 2 l^2 h, square 2 l^3, update 2 l^2 h; symmetry savings not deducted)."""
+    rows, cols = shape[-2], shape[-1]
+    l, h = min(rows, cols), max(rows, cols)
+    batch = 1
+    for d in shape[:-2]:
+        batch *= d
+    return float(batch) * steps * (4.0 * l * l * h + 2.0 * l ** 3)
+
+
+def partition_by_flops(costs: Sequence[float], world: int) -> List[int]:
+    """Longest-processing-time greedy: heaviest matrix first onto the least loaded rank.
+    Ties break toward the lower rank and the lower index, so every rank computes the
+    same assignment."""
+    order = sorted(range(len(costs)), key=lambda i: (-costs[i], i))
+    load = [0.0] * world
+    owner = [0] * len(costs)
+    for i in order:
+        r = min(range(world), key=lambda q: (load[q], q))
+        owner[i] = r
+        load[r] += costs[i]
+    return owner
+
+
+@dataclass
+class ShardGroup:
+    """Matrices of one (shape, dtypes) signature."""
+    key: Tuple
+    members: List[int]                       # indices into the parameter list
+    owner: List[int]                         # owning rank per member
+    slots: List[List[int]] = field(default_factory=list)   # per rank: members it owns, in order
+    width: int = 0                           # max matrices any rank owns in this group
+
+
+@dataclass
+class ShardPlan:
+    world: int
+    groups: List[ShardGroup]
+    load: List[float]
+
+    def owned(self, rank: int) -> List[int]:
+        return [i for g in self.groups for i in g.slots[rank]]
+
+
+def build_plan(shapes: Sequence[Sequence[int]], keys: Sequence[Tuple], world: int, steps: int) -> ShardPlan:
+    """Assign every matrix to a rank and lay out the all-gather slots per shape group."""
+    costs = [ns_flops(s, steps) for s in shapes]
+    owner = partition_by_flops(costs, world)
+    load = [0.0] * world
+    for i, r in enumerate(owner):
+        load[r] += costs[i]
+    by_key: Dict[Tuple, List[int]] = {}
+    for i, k in enumerate(keys):
+        by_key.setdefault(k, []).append(i)
+    groups = []
+    for k, members in by_key.items():
+        g = ShardGroup(key=k, members=members, owner=[owner[i] for i in members])
+        g.slots = [[i for i in members if owner[i] == r] for r in range(world)]
+        g.width = max(len(s) for s in g.slots)
+        groups.append(g)
+    return ShardPlan(world=world, groups=groups, load=load)
+
+
+@dataclass
+class StepOps:
+    """momentum(grads, bufs, out): write stacked updates of len(grads) matrices into out[:len(grads)].
+    orthogonalise(x) -> same shape.  apply(params, updates): updates is (len(params), *shape)."""
+    momentum: Callable
+    orthogonalise: Callable
+    apply: Callable
+
+
+class ShardedMuonStep:
+    """One Muon step over replicated parameters with sharded Newton-Schulz.
+
+    ``buffers`` maps parameter index -> momentum buffer and only needs entries for
+    the matrices this rank owns (``plan.owned(rank)``).
+    """
+
+    def __init__(self, params, steps: int, ops: StepOps, group=None, max_group_bytes: int = 2 << 30):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.ops = ops
+        shapes = [tuple(p.shape) for p in params]
+        keys = [(p.device.type, p.dtype, tuple(p.shape)) for p in params]
+        self.plan = build_plan(shapes, keys, self.world, steps)
+        self.max_group_bytes = max_group_bytes
+        self._staging: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+    def _buffers_for(self, g: ShardGroup, width: int, like: torch.Tensor, parity: int):
+        # two staging sets per signature: chunk n+1 is produced while chunk n is gathered and applied
+        key = (g.key, width, parity)
+        hit = self._staging.get(key)
+        if hit is None:
+            send = torch.zeros((width, *like.shape), dtype=like.dtype, device=like.device)
+            recv = torch.empty((self.world * width, *like.shape), dtype=like.dtype, device=like.device)
+            hit = self._staging[key] = (send, recv)
+        return hit
+
+    def step(self, params, grads, buffers) -> None:
+        pending = []
+        issued = 0
+        for g in self.plan.groups:
+            like = grads[g.members[0]]
+            per_matrix = like.numel() * like.element_size()
+            # bound the stacked batch: process the group's slots in column chunks
+            chunk = max(1, min(g.width, self.max_group_bytes // max(1, per_matrix)))
+            for first in range(0, g.width, chunk):
+                width = min(chunk, g.width - first)
+                mine = g.slots[self.rank][first:first + width]
+                send, recv = self._buffers_for(g, width, like, issued & 1)
+                issued += 1
+                if mine:
+                    self.ops.momentum([grads[i] for i in mine], [buffers[i] for i in mine], send)
+                    send[:len(mine)].copy_(self.ops.orthogonalise(send[:len(mine)]))
+                if self.world > 1:
+                    work = dist.all_gather_into_tensor(recv, send, group=self.group, async_op=True)
+                else:
+                    work, recv = None, send
+                pending.append((g, first, width, recv, work))
+                # apply the previous chunk while this chunk's collective is in flight
+                if len(pending) > 1:
+                    self._apply(params, *pending.pop(0))
+        while pending:
+            self._apply(params, *pending.pop(0))
+
+    def _apply(self, params, g: ShardGroup, first: int, width: int, recv, work) -> None:
+        if work is not None:
+            work.wait()
+        for r in range(self.world):
+            theirs = g.slots[r][first:first + width]
+            if theirs:
+                self.ops.apply([params[i] for i in theirs], recv[r * width:r * width + len(theirs)])

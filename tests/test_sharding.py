@@ -1,0 +1,115 @@
+"""Multi-rank step bookkeeping on CPU ranks (gloo, world size 2 and 3): the flop
+partition, the all-gather slot layout, and equality with the unsharded step."""
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from i8muon_b200.sharding import ShardedMuonStep, StepOps, build_plan, ns_flops, partition_by_flops
+from oracle import ns_oracle as o
+
+LLAMA_LAYER = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (14336, 4096), (4096, 14336)]
+
+
+def test_flop_count_matches_stated_totals():
+    total = sum(ns_flops(s, 5) for s in LLAMA_LAYER) * 32
+    assert abs(total / 6.659e14 - 1) < 1e-3          # Llama-3-8B-shaped set, 5 steps
+    assert abs(ns_flops((1024, 4096), 5) / 9.664e10 - 1) < 1e-3
+    assert ns_flops((3, 64, 32), 2) == 3 * 2 * (4 * 32 * 32 * 64 + 2 * 32 ** 3)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_partition_of_llama_set_is_balanced(world):
+    shapes = LLAMA_LAYER * 32
+    keys = [("cuda", torch.bfloat16, s) for s in shapes]
+    plan = build_plan(shapes, keys, world, 5)
+    assert max(plan.load) / (sum(plan.load) / world) < 1.0001  # exact split for 1/2/4/8 ranks
+    counts = {}
+    for g in plan.groups:
+        assert sorted(i for slot in g.slots for i in slot) == sorted(g.members)
+        assert g.width == max(len(s) for s in g.slots)
+        counts[g.key[2]] = [len(s) for s in g.slots]
+    if world == 8:
+        assert counts[(14336, 4096)] == [8] * 8 and counts[(4096, 14336)] == [4] * 8
+        assert counts[(4096, 4096)] == [8] * 8 and counts[(1024, 4096)] == [8] * 8
+
+
+def test_partition_is_deterministic_and_greedy():
+    costs = [5.0, 3.0, 3.0, 2.0, 2.0, 1.0]
+    owner = partition_by_flops(costs, 2)
+    assert owner == partition_by_flops(costs, 2)
+    loads = [sum(c for c, r in zip(costs, owner) if r == q) for q in range(2)]
+    assert loads == [8.0, 8.0]
+    assert partition_by_flops([1.0], 4) == [0]
+
+
+def cpu_ops(momentum, lr, wd, mode, adjust):
+    def do_momentum(grads, bufs, out):
+        for j, (g, b) in enumerate(zip(grads, bufs)):
+            out[j].copy_(o.momentum_update(g, b, momentum))
+
+    def do_ns(x):
+        return (x.float() * 3.0).to(x.dtype)  # stand-in, as in the golden fixtures
+
+    def do_apply(params, updates):
+        for p, u in zip(params, updates):
+            o.apply_update(p, u.clone(), lr=lr, adjusted_lr=o.adjust_lr(lr, adjust, p.shape), weight_decay=wd,
+                           weight_decay_mode=mode)
+    return StepOps(momentum=do_momentum, orthogonalise=do_ns, apply=do_apply)
+
+
+def make_problem():
+    g = torch.Generator().manual_seed(77)
+    shapes = [(24, 40), (24, 40), (24, 40), (40, 24), (2, 16, 16), (24, 40), (8, 64), (8, 64), (24, 40)]
+    params = [(torch.randn(s, generator=g) * 0.02).bfloat16() for s in shapes]
+    bufs = [(torch.randn(s, generator=g) * 1e-3).bfloat16() for s in shapes]
+    grads = [[(torch.randn(s, generator=g) * 1e-3).bfloat16() for s in shapes] for _ in range(3)]
+    return params, bufs, grads
+
+
+def expected():
+    params, bufs, grads = make_problem()
+    for step_grads in grads:
+        for p, b, g in zip(params, bufs, step_grads):
+            u = o.momentum_update(g, b, (0.95, 0.9))
+            u = (u.float() * 3.0).to(u.dtype)
+            o.apply_update(p, u, lr=0.02, adjusted_lr=o.adjust_lr(0.02, "spectral", p.shape), weight_decay=0.01,
+                           weight_decay_mode="base_lr")
+    return params, bufs
+
+
+def worker(rank, world, store_path, result_path):
+    dist.init_process_group("gloo", init_method=f"file://{store_path}", rank=rank, world_size=world)
+    try:
+        params, bufs, grads = make_problem()
+        ops = cpu_ops((0.95, 0.9), 0.02, 0.01, "base_lr", "spectral")
+        # a tiny byte budget forces several chunks per group, exercising the ping-pong staging
+        stepper = ShardedMuonStep(params, steps=5, ops=ops, max_group_bytes=2 * 24 * 40 * 2)
+        owned = set(stepper.plan.owned(rank))
+        buffers = {i: bufs[i] for i in owned}
+        for step_grads in grads:
+            stepper.step(params, step_grads, buffers)
+        torch.save(dict(params=params, owned=sorted(owned), bufs={i: bufs[i] for i in owned}),
+                   f"{result_path}.{rank}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_step_equals_unsharded(world):
+    want_params, want_bufs = expected()
+    with tempfile.TemporaryDirectory() as tmp:
+        store, result = os.path.join(tmp, "store"), os.path.join(tmp, "result")
+        mp.spawn(worker, args=(world, store, result), nprocs=world, join=True)
+        seen = set()
+        for rank in range(world):
+            got = torch.load(f"{result}.{rank}")
+            for p, w in zip(got["params"], want_params):
+                assert torch.equal(p, w)           # parameters stay replicated and correct on every rank
+            for i, b in got["bufs"].items():
+                assert torch.equal(b, want_bufs[i])  # momentum lives with its owner
+            seen |= set(got["owned"])
+        assert seen == set(range(len(want_params)))
