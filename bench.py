@@ -1,0 +1,335 @@
+"""Benchmark of the Muon step over a Llama-3-8B-shaped parameter set on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
+
+One "step" is one full optimizer step (momentum, Newton-Schulz, weight decay and
+update) over 224 synthetic matrices: 32 layers x {q 4096x4096, k 1024x4096,
+v 1024x4096, o 4096x4096, gate 14336x4096, up 14336x4096, down 4096x14336}, BF16
+weights N(0, 0.02) and gradients N(0, 1e-3), 128x128 block-quantised INT8 with
+the reference's default first FP16 iteration, five int8_safe iterations.
+
+metric  muon_step_ns_tflops: algorithmic Newton-Schulz flops of the whole set
+        (T (4 l^2 h + 2 l^3) per matrix = 6.659e14) per second of step time, all
+        ranks together; ms_per_step is the step latency.
+N > 1   launched by torch.distributed.run; matrices are partitioned across ranks
+        by flops, each rank orthogonalises its share, updates are all-gathered
+        (strong scaling: the parameter set is fixed).
+e2e     the same step with that step's gradients copied from pinned host memory
+        inside the timed region and a scalar metric read back.
+roofline  the block-quantised INT8 update GEMM timed alone with CUDA events on
+        the gate/up shape, against twice the measured BF16 tensor peak.
+cpu_baseline / --impl reference
+        the reference has no CPU implementation of this path; its README formula
+        X <- (a I + b G + c G^2) X in FP32 torch, driven by the reference's step
+        statements, is timed on the host cores on a bounded sample of the set.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LAYER = [("q", 4096, 4096), ("k", 1024, 4096), ("v", 1024, 4096), ("o", 4096, 4096),
+         ("gate", 14336, 4096), ("up", 14336, 4096), ("down", 4096, 14336)]
+NS_STEPS = 5
+LR, WD, MOMENTUM = 0.02, 0.01, (0.95, 0.95)
+
+
+def shapes(layers: int):
+    return [(rows, cols) for _ in range(layers) for _, rows, cols in LAYER]
+
+
+def ns_flops_of(shape_list):
+    from i8muon_b200.sharding import ns_flops
+    return sum(ns_flops(s, NS_STEPS) for s in shape_list)
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return data, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples during the timed region."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [line.split(",") for line in Path(self.file.name).read_text().splitlines() if line.count(",") >= 8]
+        os.unlink(self.file.name)
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in rows:
+            try:
+                clocks.append(float(row[1]))
+                maxima.append(float(row[2]))
+            except ValueError:
+                continue
+            for name, value in zip(names, row[5:9]):
+                if value.strip().lower().startswith("active"):
+                    reasons.add(name)
+        busy = [c for c in clocks if c > 0.5 * max(clocks)] if clocks else []
+        return {"sm_mhz": statistics.median(busy) if busy else None,
+                "sm_max_mhz": max(maxima) if maxima else None, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_sample_step(sample, coeffs):
+    """The reference's step statements on CPU tensors with the FP32 torch Newton-Schulz."""
+    from oracle import ns_oracle as o
+    for p, g, b in sample:
+        u = o.momentum_update(g, b, MOMENTUM)
+        u = o.ns_fp32_torch(u, coeffs)
+        o.apply_update(p, u, lr=LR, adjusted_lr=o.adjust_lr(LR, "match_rms_adamw", p.shape), weight_decay=WD,
+                       weight_decay_mode="base_lr")
+
+
+def make_cpu_sample():
+    gen = torch.Generator().manual_seed(4000)
+    sample_shapes = [(1024, 4096), (4096, 4096)]
+    sample = []
+    for s in sample_shapes:
+        p = (torch.randn(s, generator=gen) * 0.02).bfloat16()
+        g = (torch.randn(s, generator=gen) * 1e-3).bfloat16()
+        sample.append((p, g, torch.zeros_like(g)))
+    return sample, sample_shapes
+
+
+def time_cpu(steps: int, warmup: int):
+    from i8muon_b200 import recommend_coefficients
+    torch.set_num_threads(os.cpu_count() or 1)
+    coeffs = recommend_coefficients(NS_STEPS)
+    sample, sample_shapes = make_cpu_sample()
+    for _ in range(warmup):
+        cpu_sample_step(sample, coeffs)
+    start = time.perf_counter()
+    for _ in range(steps):
+        cpu_sample_step(sample, coeffs)
+    seconds = (time.perf_counter() - start) / steps
+    flops = ns_flops_of(sample_shapes)
+    return {"value": flops / seconds / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": "one k (1024x4096) and one q (4096x4096) matrix per step, FP32 torch NS, "
+                      f"{flops:.3e} flop, {seconds:.2f} s/step", "seconds_per_step": seconds}
+
+
+def config_dict(world: int, layers: int, precision: str, fp16_first: bool):
+    return {"workload": f"llama3-8b-shaped parameter set, {layers} layers x 7 matrices, bf16, "
+                        f"precision={precision}, fp16_first={fp16_first}, ns_steps={NS_STEPS} int8_safe",
+            "matrices": layers * len(LAYER), "ns_steps": NS_STEPS, "precision": precision,
+            "fp16_first": fp16_first, "parallelism": f"flop-partitioned x{world} + all-gather of updates",
+            "l2": "inputs (3 x 14 GB) are larger than L2; no flush needed"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 5))
+    cpu = time_cpu(steps, min(args.warmup, 1))
+    line = {"impl": "reference", "metric": "muon_step_ns_tflops", "value": cpu["value"], "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+            "ms_per_step": cpu["seconds_per_step"] * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_dict(args.gpus, args.layers, args.precision, bool(args.fp16_first)),
+            "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": cpu["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference has no CPU implementation of this path (it refuses non-CUDA tensors); this is "
+                    "its README formula in FP32 torch under its own step statements, on a bounded sample"}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def dominant_kernel_roofline(dev, peaks, source):
+    """Time the INT8 block-quantised update GEMM alone on the gate/up shape."""
+    from i8muon_b200 import native
+    from i8muon_b200.engine import status_word
+    b, lp, hp = 4, 4096, 14336
+    gen = torch.Generator(device=dev).manual_seed(5)
+    pq = torch.randint(-127, 128, (b, lp, lp), device=dev, dtype=torch.int8, generator=gen)
+    at = torch.randint(-127, 128, (b, hp, lp), device=dev, dtype=torch.int8, generator=gen)
+    a = at.mT.contiguous()
+    sp = torch.rand((b, lp // 128, lp // 128), device=dev, generator=gen) * 1e-3 + 1e-4
+    sa = torch.rand((b, lp // 128, hp // 128), device=dev, generator=gen) * 1e-3 + 1e-4
+    dp = torch.rand((b, lp), device=dev, generator=gen)
+    y, yt = torch.empty_like(a), torch.empty_like(at)
+    sy = torch.empty_like(sa)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch():
+        native.call("i8m_bq_gemm", 0, 2, pq.data_ptr(), sp.data_ptr(), dp.data_ptr(), at.data_ptr(), sa.data_ptr(),
+                    a.data_ptr(), y.data_ptr(), yt.data_ptr(), sy.data_ptr(), None, b, lp, hp, lp, lp, hp, 0.0, 0.0,
+                    0.0, 0, 0, 0, status_word(dev).data_ptr(), stream)
+    for _ in range(3):
+        launch()
+    n = 10
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(n):
+        launch()
+    end.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(end) / 1e3 / n
+    flops = 2.0 * lp * lp * hp * b
+    achieved = flops / seconds / 1e12
+    peak = 2.0 * peaks["bf16_tflops_sustained"]
+    return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "traffic": None, "kernel": "ns_gemm_kernel<EpiBq<int8, update>> B=4 4096x14336 (k=4096)",
+            "flops_per_launch": flops, "ms_per_launch": seconds * 1e3,
+            "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({source}); INT8 dense rate is twice BF16"}
+
+
+def run_native(args):
+    import torch.distributed as dist
+    from i8muon_b200 import CutlassNSInt8, check_status, native, recommend_coefficients
+    from i8muon_b200.optimizer import native_step_ops
+    from i8muon_b200.sharding import ShardedMuonStep
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    shape_list = shapes(args.layers)
+    total_flops = ns_flops_of(shape_list)
+    coeffs = recommend_coefficients(NS_STEPS)
+    engine = CutlassNSInt8(fp16_first=bool(args.fp16_first))
+    ops = native_step_ops(engine, lr=LR, weight_decay=WD, momentum=MOMENTUM, ns_coefficients=coeffs,
+                          adjust_lr_fn="match_rms_adamw", precision=args.precision, use_gram=False)
+    gen = torch.Generator(device=dev).manual_seed(4000)  # same seed on every rank: replicated tensors
+    params = [(torch.randn(s, device=dev, generator=gen) * 0.02).bfloat16() for s in shape_list]
+    grads = [(torch.randn(s, device=dev, generator=gen) * 1e-3).bfloat16() for s in shape_list]
+    stepper = ShardedMuonStep(params, NS_STEPS, ops, max_group_bytes=args.group_bytes)
+    buffers = {i: torch.zeros_like(grads[i]) for i in stepper.plan.owned(rank)}
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, count):
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(count):
+            fn()
+        end.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(end)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item() / 1e3
+
+    step = lambda: stepper.step(params, grads, buffers)  # noqa: E731
+    for _ in range(args.warmup):
+        step()
+    check_status()
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches_before = native.launch_count()
+    seconds = timed(step, args.steps)
+    launches = native.launch_count() - launches_before
+    clocks = sampler.stop() if sampler else None
+    check_status()
+
+    # end to end: this step's gradients arrive from pinned host memory, a scalar comes back
+    pinned = torch.empty(256 << 20, dtype=torch.bfloat16).pin_memory()
+    pinned.normal_(0, 1e-3)
+    result_host = torch.empty(1, dtype=torch.float32).pin_memory()
+    h2d = sum(g.numel() * g.element_size() for g in grads)
+
+    def e2e_step():
+        for g in grads:
+            flat = g.view(-1)
+            for off in range(0, flat.numel(), pinned.numel()):
+                part = min(pinned.numel(), flat.numel() - off)
+                flat[off:off + part].copy_(pinned[:part], non_blocking=True)
+        stepper.step(params, grads, buffers)
+        result_host.copy_(params[0].float().norm().reshape(1), non_blocking=True)
+    e2e_steps = max(1, min(args.steps, 2))
+    e2e_step()
+    e2e_seconds = timed(e2e_step, e2e_steps)
+    check_status()
+
+    launch_total = torch.tensor([float(launches)], device=dev)
+    if world > 1:
+        dist.all_reduce(launch_total)
+    peaks, source = measured_peaks()
+    roofline = dominant_kernel_roofline(dev, peaks, source) if rank == 0 else None
+    cpu = time_cpu(1, 0) if (rank == 0 and world == 1 and not args.no_cpu) else None
+    if rank == 0:
+        value = total_flops * args.steps / seconds / 1e12
+        line = {"metric": "muon_step_ns_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "s8",
+                "data": "synthetic", "config": config_dict(world, args.layers, args.precision, bool(args.fp16_first)),
+                "algorithmic_flops_per_step": total_flops,
+                "frac_of_int8_peak": value / world / (2.0 * peaks["bf16_tflops_sustained"]),
+                "e2e": {"value": total_flops * e2e_steps / e2e_seconds / 1e12, "unit": "TFLOP/s",
+                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                        "ms_per_step": e2e_seconds / e2e_steps * 1e3, "steps": e2e_steps},
+                "gpu_launches": int(launch_total.item()), "clocks": clocks, "roofline": roofline}
+        if cpu is not None:
+            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=3)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=("native", "reference"), default="native")
+    parser.add_argument("--precision", default="int8_bq")
+    parser.add_argument("--fp16-first", type=int, default=1)
+    parser.add_argument("--layers", type=int, default=32, help="layers of the parameter set (32 = the full set)")
+    parser.add_argument("--group-bytes", type=int, default=2 << 30)
+    parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

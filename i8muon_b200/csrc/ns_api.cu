@@ -10,6 +10,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -21,6 +22,7 @@ namespace {
 
 thread_local char g_error[512] = "";
 int g_debug_simt = 0;
+std::atomic<unsigned long long> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -40,6 +42,7 @@ int fail(int code, const char* fmt, ...) {
     cudaError_t e_ = cudaGetLastError();                                            \
     if (e_ != cudaSuccess)                                                          \
       return fail(I8M_E_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e_)); \
+    g_launches.fetch_add(1, std::memory_order_relaxed);                             \
   } while (0)
 
 inline cudaStream_t S(i8m_stream_t s) { return static_cast<cudaStream_t>(s); }
@@ -181,6 +184,7 @@ extern "C" const char* i8m_build_info(void) {
   return info;
 }
 extern "C" const char* i8m_last_error(void) { return g_error; }
+extern "C" unsigned long long i8m_launch_count(void) { return g_launches.load(); }
 extern "C" int i8m_set_debug_core(int simt) {
   g_debug_simt = simt ? 1 : 0;
   return 0;

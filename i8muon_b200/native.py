@@ -8,7 +8,7 @@ one, and raises :class:`NativeError` on a negative return code.
 from __future__ import annotations
 
 import ctypes
-from ctypes import (POINTER, c_char_p, c_double, c_float, c_int, c_longlong, c_size_t, c_uint32,
+from ctypes import (POINTER, c_char_p, c_double, c_float, c_int, c_longlong, c_size_t, c_ulonglong,
                     c_void_p)
 from functools import lru_cache
 
@@ -27,6 +27,7 @@ _SIGNATURES = {
     "i8m_version": (c_int, []),
     "i8m_build_info": (c_char_p, []),
     "i8m_last_error": (c_char_p, []),
+    "i8m_launch_count": (c_ulonglong, []),
     "i8m_set_debug_core": (c_int, [c_int]),
     "i8m_stats_scratch_bytes": (c_int, [c_int, c_longlong, POINTER(c_size_t)]),
     "i8m_stats": (c_int, [_P, c_int, c_int, c_longlong, _P, c_size_t, _P, _P, _P]),
@@ -109,6 +110,10 @@ def stats_scratch_bytes(batch, count) -> int:
     size = c_size_t(0)
     call("i8m_stats_scratch_bytes", batch, count, ctypes.byref(size))
     return size.value
+
+
+def launch_count() -> int:
+    return int(library().i8m_launch_count())
 
 
 def build_info() -> str:

@@ -54,6 +54,9 @@ int i8m_version(void);
 const char* i8m_build_info(void);
 /* message of the last failing call on this thread; static storage */
 const char* i8m_last_error(void);
+/* number of kernels this library has launched in this process (every stage kernel
+ * and GEMM counts once; memsets do not); used to report launches per step */
+unsigned long long i8m_launch_count(void);
 /* tests only: 1 replaces the TMA/tcgen05 mainloop by plain dot products inside
  * the epilogue threads (same epilogues); 0 restores the tensor-core path. */
 int i8m_set_debug_core(int simt);

@@ -94,7 +94,8 @@ def test_gram_restart_orders_and_polar_express(cuda_device, monkeypatch):
     ref = o.ns_float(x, PE8, 1e-7, "float16", gram=True, order="00100", norm=kernel_norm(x, cuda_device))
     truth = o.ns_fp32_torch(x, PE8)
     assert rel(y.float(), truth) < 1.5 * rel(ref.float(), truth) + 1e-2
-    assert np.all(np.abs(sigma(y) - sigma(ref)) < 5e-2)
+    # singular values no further from the exact iteration's than the oracle's are
+    assert np.all(np.abs(sigma(y) - sigma(truth)) <= np.abs(sigma(ref) - sigma(truth)) + 2e-2)
     monkeypatch.setenv("I8MUON_GRAM_RESET", "10")
     with pytest.raises(ValueError):
         engine._gram_prec(x.to(cuda_device), PE8, 1e-7, True, "float16")
