@@ -213,6 +213,55 @@ extern "C" int i8m_stats(const void* x, int dtype, int batch, long long count, v
   return 0;
 }
 
+// ------------------------------------------------------ stats without allocation
+// Scratch for i8m_stats_static lives in the library image: 2^20 floats (4 MiB) per GPU
+// that loads the library, held until the process exits.
+constexpr size_t STATIC_SCRATCH_FLOATS = size_t(1) << 20;
+static __device__ __align__(256) float g_static_stats_scratch[STATIC_SCRATCH_FLOATS];
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_ptr[MAX_DEVICES] = {};
+std::mutex g_static_scratch_mutex;
+}  // namespace
+
+extern "C" int i8m_stats_static(const void* x, int dtype, int batch, long long count, float* norm,
+                                float* amax, i8m_stream_t stream) {
+  if (!x || batch < 1 || batch > 65535 || count < 1 || !float_dtype_ok(dtype))
+    return fail(I8M_E_ARGUMENT, "stats_static: bad argument");
+  const long long chunks = (count + STATS_CHUNK - 1) / STATS_CHUNK;
+  const unsigned long long need = 2ull * (unsigned long long)batch * (unsigned long long)chunks;
+  if (need > STATIC_SCRATCH_FLOATS)
+    return fail(I8M_E_LIMIT,
+                "stats_static: batch * ceil(count / 8192) = %lld exceeds the built-in scratch of %zu "
+                "partials; use i8m_stats with caller scratch",
+                (long long)batch * chunks, STATIC_SCRATCH_FLOATS / 2);
+  int device = -1;
+  CUDA_TRY(cudaGetDevice(&device));
+  if (device < 0 || device >= MAX_DEVICES) return fail(I8M_E_LIMIT, "stats_static: device index %d", device);
+  float* scratch = nullptr;
+  {
+    // First call on this device: resolve the device address of the array.  In host
+    // code the array's name is only a handle, never a pointer a kernel may use.
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_ptr[device]) {
+      void* address = nullptr;
+      CUDA_TRY(cudaGetSymbolAddress(&address, g_static_stats_scratch));
+      g_static_scratch_ptr[device] = static_cast<float*>(address);
+    }
+    scratch = g_static_scratch_ptr[device];
+  }
+  // Every partial that the second pass reads is written by the first pass of the
+  // same call, so nothing left over from an earlier call needs clearing.
+  float* psum = scratch;
+  float* pmax = scratch + size_t(batch) * chunks;
+  DISPATCH_IN(dtype, In, (stats_partial_kernel<In><<<dim3(unsigned(chunks), batch), STATS_THREADS, 0, S(stream)>>>(
+                             static_cast<const In*>(x), psum, pmax, count, int(chunks))));
+  LAUNCH_CHECK("stats_partial(static)");
+  stats_final_kernel<<<batch, STATS_THREADS, 0, S(stream)>>>(psum, pmax, norm, amax, int(chunks));
+  LAUNCH_CHECK("stats_final(static)");
+  return 0;
+}
+
 // ========================================================== floating path
 extern "C" int i8m_normalize(const void* x, int in_dtype, const float* norm, void* a, void* a_t,
                              void* a_lo, void* a_t_lo, int compute, int batch, int rows, int cols,

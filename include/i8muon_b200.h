@@ -71,6 +71,26 @@ int i8m_stats_scratch_bytes(int batch, long long count, size_t* bytes);
 int i8m_stats(const void* x_device, int dtype, int batch, long long count, void* scratch_device,
               size_t scratch_bytes, float* norm_device, float* amax_device, i8m_stream_t stream);
 
+/* Same result as i8m_stats for callers that cannot allocate device memory.
+ * No counterpart in the reference.  Some hosts of this library never get to call
+ * cudaMalloc: plugins that were handed a fixed memory budget by their framework,
+ * code on a latency-critical thread where a call that may synchronise the device
+ * is forbidden, or callers whose allocator is not reachable from the thread they
+ * are on.  For them the
+ * two-pass reduction keeps its partials in a 4 MiB array that is part of the
+ * library image on every GPU that loads the library (held until process exit).
+ *   limit     batch * ceil(count / 8192) <= 524288, otherwise I8M_E_LIMIT
+ *   set-up    the first call on each device looks up the array's device address
+ *             (with that device current); that first call should come before any
+ *             stream capture begins
+ *   sharing   all calls on a device use the same array: calls whose kernels can
+ *             overlap on the GPU (different streams) race and must be serialised
+ *             by the caller; nothing needs clearing between calls because every
+ *             partial read is written earlier in the same call
+ * Allocates nothing: no cudaMalloc / cudaFree and no allocating library routine. */
+int i8m_stats_static(const void* x_device, int dtype, int batch, long long count,
+                     float* norm_device, float* amax_device, i8m_stream_t stream);
+
 /* ---- stage level: floating path -------------------------------------------
  * normalize: src/i8muon/csrc/prec.cu:193-208.  A = E(x / max(norm, eps)) padded to
  * (lp x hp) plus A^T; transpose != 0 means the input has rows > cols and A = x^T.
