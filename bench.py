@@ -172,11 +172,11 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------- GPU arm
-def dominant_kernel_roofline(dev, peaks, source):
+def dominant_kernel_roofline(dev, peaks, source, b=4):
     """Time the INT8 block-quantised update GEMM alone on the gate/up shape."""
     from i8muon_b200 import native
     from i8muon_b200.engine import status_word
-    b, lp, hp = 4, 4096, 14336
+    lp, hp = 4096, 14336
     gen = torch.Generator(device=dev).manual_seed(5)
     pq = torch.randint(-127, 128, (b, lp, lp), device=dev, dtype=torch.int8, generator=gen)
     at = torch.randint(-127, 128, (b, hp, lp), device=dev, dtype=torch.int8, generator=gen)
@@ -207,7 +207,7 @@ def dominant_kernel_roofline(dev, peaks, source):
     achieved = flops / seconds / 1e12
     peak = 2.0 * peaks["bf16_tflops_sustained"]
     return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-            "traffic": None, "kernel": "ns_gemm_kernel<EpiBq<int8, update>> B=4 4096x14336 (k=4096)",
+            "traffic": None, "kernel": f"ns_gemm_kernel<EpiBq<int8, update>> B={b} 4096x14336 (k=4096)",
             "flops_per_launch": flops, "ms_per_launch": seconds * 1e3,
             "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({source}); INT8 dense rate is twice BF16"}
 
@@ -324,7 +324,14 @@ def main():
     parser.add_argument("--layers", type=int, default=32, help="layers of the parameter set (32 = the full set)")
     parser.add_argument("--group-bytes", type=int, default=2 << 30)
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--only-roofline", type=int, default=0, metavar="B",
+                        help="only time the dominant GEMM on B matrices of 4096x14336 (small case for ncu)")
     args = parser.parse_args()
+    if args.only_roofline:
+        torch.cuda.set_device(0)
+        peaks, source = measured_peaks()
+        print(json.dumps(dominant_kernel_roofline(torch.device("cuda", 0), peaks, source, args.only_roofline)))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

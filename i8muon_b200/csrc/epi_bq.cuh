@@ -12,6 +12,16 @@
 // then (non-final) tile max (floor 1e-8) -> scale, quantise (INT8 truncates toward
 // zero, E4M3 rounds to nearest even and saturates), store the tile and its
 // mirror / transpose; the final update casts to the user's dtype instead.
+//
+// How the promotion keeps up with the tensor core (one K block is ~270 cycles of
+// tcgen05.mma; 128 x 128 partials have to be folded in that time by four warps):
+//   * int32 -> FP32 without the conversion unit: each TMEM buffer is preset to the
+//     bit pattern of 1.5 * 2^23 and the MMA accumulates on top of it, so what the
+//     epilogue loads IS the float 12582912 + partial (|partial| <= 128 * 127^2 < 2^22);
+//     one exact subtraction recovers float(partial);
+//   * that subtraction and the fmaf run as packed two-lane FP32 instructions
+//     (add.rn.f32x2 / fma.rn.f32x2), halving the issue slots;
+//   * four TMEM buffers (all 512 columns) decouple the two sides.
 #pragma once
 #include "epi_float.cuh"
 
@@ -48,6 +58,29 @@ __device__ __forceinline__ uint8_t bq_quant(float v, float multiplier) {
   }
 }
 
+// packed two-lane FP32 arithmetic (sm_100): one issue slot for two IEEE operations
+__device__ __forceinline__ unsigned long long pack2(uint32_t lo, uint32_t hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
+                                                   unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ float lane0(unsigned long long v) { return __uint_as_float(uint32_t(v)); }
+__device__ __forceinline__ float lane1(unsigned long long v) { return __uint_as_float(uint32_t(v >> 32)); }
+
+constexpr uint32_t I8_MAGIC_BITS = 0x4B400000u;  // 1.5 * 2^23 = 12582912.0f
+constexpr float I8_MAGIC = 12582912.0f;
+
 template <bool FP8, int MODE>
 struct EpiBq {
   static constexpr int KIND = FP8 ? KIND_F8 : KIND_I8;
@@ -55,6 +88,8 @@ struct EpiBq {
   static constexpr int PARTS = 1;
   static constexpr bool BLOCKQ = true;
   static constexpr int PROMOTE_KB = 1;
+  static constexpr int NBUF = 4;           // TMEM accumulators of 128 columns
+  static constexpr bool PRESET = !FP8;     // INT8: accumulators start at the bias constant
   static constexpr int STAGES = 4;
   static constexpr int MIN_CTAS = 1;
   static constexpr uint32_t IDESC =
@@ -62,107 +97,188 @@ struct EpiBq {
   using Args = BqArgs;
   static constexpr float QMAX = FP8 ? 448.f : 127.f;
 
+  static __device__ __forceinline__ float block_scale(const GemmGeom& g, const Args& a,
+                                                      const TileCtx& t, int kb, int mq, int nq,
+                                                      int kq) {
+    float bs;
+    if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
+      bs = a.sb[(size_t(t.b) * kq + kb) * nq + t.tn];
+    else
+      bs = a.sb[(size_t(t.b) * nq + t.tn) * kq + kb];
+    return __fmul_rn(a.sa[(size_t(t.b) * mq + t.tm) * kq + kb], bs);
+  }
+
+  template <bool DEBUG>
   static __device__ __forceinline__ void run_blockq(const GemmGeom& g, const Args& a,
                                                     const TileCtx& t, uint32_t taddr,
                                                     volatile uint32_t* abort_flag) {
     constexpr int Q = TILE;
     const int mq = g.m / Q, nq = g.n / Q, kq = g.k / Q;
-    float total[Q];
+    unsigned long long tot[Q / 2];
 #pragma unroll
-    for (int j = 0; j < Q; ++j) total[j] = 0.f;
+    for (int j = 0; j < Q / 2; ++j) tot[j] = 0ull;
     bool ok = true;
+    if constexpr (DEBUG) {
+      // debug core: plain dot products per K block, same promotion arithmetic
 #pragma unroll 1
-    for (int kb = 0; kb < g.num_kb; ++kb) {
-      const int buf = kb & 1;
-      if (!g.debug_simt) {
-        ok = mbar_wait(smem_u32(&t.ctrl->acc_full[buf]), uint32_t(kb >> 1) & 1u, abort_flag);
+      for (int kb = 0; kb < g.num_kb; ++kb) {
+        const float s = block_scale(g, a, t, kb, mq, nq, kq);
+#pragma unroll 4
+        for (int j = 0; j < Q / 2; ++j) {
+          uint32_t v0 = simt_dot<KIND, uint8_t>(g, t.b, t.row, t.col0 + 2 * j, kb * Q, kb * Q + Q);
+          uint32_t v1 = simt_dot<KIND, uint8_t>(g, t.b, t.row, t.col0 + 2 * j + 1, kb * Q, kb * Q + Q);
+          float p0 = FP8 ? __uint_as_float(v0) : float(int(v0));
+          float p1 = FP8 ? __uint_as_float(v1) : float(int(v1));
+          tot[j] = pack2(__float_as_uint(__fmaf_rn(p0, s, lane0(tot[j]))),
+                         __float_as_uint(__fmaf_rn(p1, s, lane1(tot[j]))));
+        }
+      }
+    } else {
+      if constexpr (PRESET) {
+        // fill every accumulator with the bias constant, then hand them to the MMA warp
+#pragma unroll
+        for (int c = 0; c < NBUF * Q / 32; ++c) tmem_st32_fill(taddr + uint32_t(c * 32), I8_MAGIC_BITS);
+        tmem_wait_st();
+        tc_fence_before();
+#pragma unroll
+        for (int i = 0; i < NBUF; ++i) mbar_arrive(smem_u32(&t.ctrl->acc_empty[i]));
+      }
+      const unsigned long long neg_magic = pack2(__float_as_uint(-I8_MAGIC), __float_as_uint(-I8_MAGIC));
+#pragma unroll 1
+      for (int kb = 0; kb < g.num_kb; ++kb) {
+        const int buf = kb % NBUF;
+        const float s = block_scale(g, a, t, kb, mq, nq, kq);
+        const unsigned long long s2 = pack2(__float_as_uint(s), __float_as_uint(s));
+        ok = mbar_wait(smem_u32(&t.ctrl->acc_full[buf]), uint32_t(kb / NBUF) & 1u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);  // keep the warp together for tcgen05.ld
         if (!ok) break;
         tc_fence_after();
-      }
-      float bs;
-      if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
-        bs = a.sb[(size_t(t.b) * kq + kb) * nq + t.tn];
-      else
-        bs = a.sb[(size_t(t.b) * nq + t.tn) * kq + kb];
-      const float s = __fmul_rn(a.sa[(size_t(t.b) * mq + t.tm) * kq + kb], bs);
+        const bool refill = PRESET && (kb + NBUF < g.num_kb);
 #pragma unroll
-      for (int c = 0; c < Q / 32; ++c) {
-        uint32_t v[32];
-        if (g.debug_simt) {
-#pragma unroll 1
-          for (int j = 0; j < 32; ++j)
-            v[j] = simt_dot<KIND, uint8_t>(g, t.b, t.row, t.col0 + c * 32 + j, kb * Q, kb * Q + Q);
-        } else {
+        for (int c = 0; c < Q / 32; ++c) {
+          uint32_t v[32];
           tmem_ld32(taddr + uint32_t(buf * Q + c * 32), v);
           tmem_wait_ld();
-        }
+          if (refill) tmem_st32_fill(taddr + uint32_t(buf * Q + c * 32), I8_MAGIC_BITS);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float p = FP8 ? __uint_as_float(v[j]) : float(int(v[j]));
-          total[c * 32 + j] = __fmaf_rn(p, s, total[c * 32 + j]);
+          for (int j = 0; j < 16; ++j) {
+            unsigned long long p = pack2(v[2 * j], v[2 * j + 1]);
+            if constexpr (PRESET) p = add2(p, neg_magic);  // exact: float(partial)
+            tot[c * 16 + j] = fma2(p, s2, tot[c * 16 + j]);
+          }
         }
-      }
-      if (!g.debug_simt) {
+        if (refill) tmem_wait_st();
         tc_fence_before();
         mbar_arrive(smem_u32(&t.ctrl->acc_empty[buf]));
       }
-    }
-    if (!ok) {
-      if (t.lane == 0)
+      if (!ok && t.lane == 0)
         atomicCAS(g.status, 0u, unsigned(ST_EPILOGUE_TIMEOUT) | unsigned(blockIdx.x & 0xff));
-      return;
     }
+    float vals[Q];
+#pragma unroll
+    for (int j = 0; j < Q / 2; ++j) { vals[2 * j] = lane0(tot[j]); vals[2 * j + 1] = lane1(tot[j]); }
+    // A warp that gave up still walks through the tail's barriers, without storing.
+    tail(g, a, t, vals, ok, mq, nq, kq);
+  }
 
-    // ------------------------------------------------------------ tile tail
+  // ---------------------------------------------------------------- tile tail
+  static __device__ __forceinline__ void tail(const GemmGeom& g, const Args& a, const TileCtx& t,
+                                              float (&vals)[TILE], const bool live, int mq, int nq,
+                                              int kq) {
+    constexpr int Q = TILE;
     const bool in_rows = t.row < g.lm;
     float drow = 0.f, stile = 0.f;
     if constexpr (MODE != BQ_GRAM) drow = a.da[size_t(t.b) * g.m + t.row];
-    if constexpr (MODE == BQ_POLY) stile = a.sa[(size_t(t.b) * mq + t.tm) * kq + t.tn];
+    if constexpr (MODE == BQ_POLY) {
+      stile = a.sa[(size_t(t.b) * mq + t.tm) * kq + t.tn];
+      // the column diagonals of this tile, shared through shared memory
+      t.ctrl->diag[t.r] = a.da[size_t(t.b) * g.m + t.col0 + t.r];
+      named_bar_sync(1, 128);
+    }
     if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
       stile = a.sb[(size_t(t.b) * kq + t.tm) * nq + t.tn];
+    // companion operand bytes of this thread's row: G (poly) or A (update), 128 contiguous bytes
+    const uint4* comp = nullptr;
+    if constexpr (MODE == BQ_POLY)
+      comp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(g.a_raw) +
+                                            (size_t(t.b) * g.m + t.row) * g.k + t.col0);
+    if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
+      comp = reinterpret_cast<const uint4*>(a.row_b + (size_t(t.b) * g.m + t.row) * g.n + t.col0);
+
     float mx = 1e-8f;
 #pragma unroll
-    for (int j = 0; j < Q; ++j) {
-      const int col = t.col0 + j;
-      float val = total[j];
-      if constexpr (MODE == BQ_GRAM) {
-        if (col == t.row) {
-          a.dout[size_t(t.b) * g.m + t.row] = in_rows ? val : 0.f;
-          val = 0.f;
-        }
-      } else if constexpr (MODE == BQ_POLY) {
-        const uint8_t gq = static_cast<const uint8_t*>(g.a_raw)[(size_t(t.b) * g.m + t.row) * g.k + col];
-        const float v = __fmul_rn(bq_decode<FP8>(gq), stile);
-        const float dcol = a.da[size_t(t.b) * g.m + col];
-        val = __fadd_rn(val, __fmul_rn(__fadd_rn(drow, dcol), v));
-        val = __fmul_rn(val, a.cc);
-        val = __fadd_rn(val, __fmul_rn(v, a.cb));
-        if (col == t.row) {
-          const float dpoly =
-              __fadd_rn(a.ca, __fmul_rn(drow, __fadd_rn(a.cb, __fmul_rn(drow, a.cc))));
-          a.dout[size_t(t.b) * g.m + t.row] = in_rows ? __fadd_rn(val, dpoly) : 0.f;
-          val = 0.f;
-        }
-      } else {
-        const uint8_t aq = a.row_b[(size_t(t.b) * g.m + t.row) * g.n + col];
-        val = __fadd_rn(val, __fmul_rn(__fmul_rn(bq_decode<FP8>(aq), drow), stile));
+    for (int c16 = 0; c16 < Q / 16; ++c16) {
+      uint32_t words[4] = {0u, 0u, 0u, 0u};
+      if constexpr (MODE != BQ_GRAM) {
+        const uint4 w = comp[c16];
+        words[0] = w.x; words[1] = w.y; words[2] = w.z; words[3] = w.w;
       }
-      if (!in_rows || col >= g.ln) val = 0.f;  // padding never contributes to a block scale
-      total[j] = val;
-      mx = fmaxf(mx, fabsf(val));
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        const int j = c16 * 16 + jj;
+        const int col = t.col0 + j;
+        float val = vals[j];
+        if constexpr (MODE == BQ_GRAM) {
+          if (col == t.row) {
+            if (live) a.dout[size_t(t.b) * g.m + t.row] = in_rows ? val : 0.f;
+            val = 0.f;
+          }
+        } else {
+          const uint8_t q = uint8_t(words[jj >> 2] >> (8 * (jj & 3)));
+          if constexpr (MODE == BQ_POLY) {
+            const float v = __fmul_rn(bq_decode<FP8>(q), stile);
+            const float dcol = t.ctrl->diag[j];
+            val = __fadd_rn(val, __fmul_rn(__fadd_rn(drow, dcol), v));
+            val = __fmul_rn(val, a.cc);
+            val = __fadd_rn(val, __fmul_rn(v, a.cb));
+            if (col == t.row) {
+              const float dpoly =
+                  __fadd_rn(a.ca, __fmul_rn(drow, __fadd_rn(a.cb, __fmul_rn(drow, a.cc))));
+              if (live) a.dout[size_t(t.b) * g.m + t.row] = in_rows ? __fadd_rn(val, dpoly) : 0.f;
+              val = 0.f;
+            }
+          } else {
+            val = __fadd_rn(val, __fmul_rn(__fmul_rn(bq_decode<FP8>(q), drow), stile));
+          }
+        }
+        if (!in_rows || col >= g.ln) val = 0.f;  // padding never contributes to a block scale
+        mx = fmaxf(mx, fabsf(val));
+        vals[j] = val;
+      }
     }
 
     if constexpr (MODE == BQ_UPDATE_FINAL) {
-      if (in_rows) {
+      if (!live || !in_rows) return;
+      const size_t rbase = (size_t(t.b) * g.lm + t.row) * g.ln + t.col0;
+      const bool wide16 = !a.transpose && a.out_dtype != DT_F32 && (g.ln % 8) == 0 && t.col0 + Q <= g.ln &&
+                          (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
+      if (wide16) {
+        // this thread's 128 consecutive 16-bit outputs as sixteen 16-byte stores
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + rbase);
 #pragma unroll
-        for (int j = 0; j < Q; ++j) {
-          const int col = t.col0 + j;
-          if (col < g.ln) {
-            size_t idx = a.transpose ? (size_t(t.b) * g.ln + col) * g.lm + t.row
-                                     : (size_t(t.b) * g.lm + t.row) * g.ln + col;
-            store_user(a.out, a.out_dtype, idx, total[j]);
+        for (int c8 = 0; c8 < Q / 8; ++c8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float lo = vals[c8 * 8 + 2 * e], hi = vals[c8 * 8 + 2 * e + 1];
+            if (a.out_dtype == DT_BF16) {
+              w[e] = uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
+                     (uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
+            } else {
+              w[e] = uint32_t(__half_as_ushort(__float2half_rn(lo))) |
+                     (uint32_t(__half_as_ushort(__float2half_rn(hi))) << 16);
+            }
           }
+          dst[c8] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        return;
+      }
+#pragma unroll
+      for (int j = 0; j < Q; ++j) {
+        const int col = t.col0 + j;
+        if (col < g.ln) {
+          size_t idx = a.transpose ? (size_t(t.b) * g.ln + col) * g.lm + t.row : rbase + j;
+          store_user(a.out, a.out_dtype, idx, vals[j]);
         }
       }
       return;
@@ -170,6 +286,7 @@ struct EpiBq {
       mx = warp_max(mx);
       if (t.lane == 0) t.ctrl->red[t.q] = mx;
       named_bar_sync(1, 128);
+      if (!live) return;
       mx = fmaxf(fmaxf(t.ctrl->red[0], t.ctrl->red[1]), fmaxf(t.ctrl->red[2], t.ctrl->red[3]));
       const float multiplier = QMAX / mx;
       const float scale = 1.f / multiplier;
@@ -179,36 +296,33 @@ struct EpiBq {
       }
       uint8_t* out = static_cast<uint8_t*>(a.out);
       const bool diag_tile = (MODE != BQ_UPDATE) && t.tm == t.tn;
-      if (!diag_tile) {
-        uint32_t packed[Q / 4];
+      // transposed target: A^T (update) or the mirrored tile (gram / poly)
+      uint8_t* tdst = (MODE == BQ_UPDATE) ? static_cast<uint8_t*>(a.out_t) : out;
+      const int trows = (MODE == BQ_UPDATE) ? g.n : g.m;
+      const int tld = (MODE == BQ_UPDATE) ? g.m : g.n;
+      uint4* dst = reinterpret_cast<uint4*>(out + (size_t(t.b) * g.m + t.row) * g.n + t.col0);
 #pragma unroll
-        for (int j = 0; j < Q; j += 4) {
-          packed[j / 4] = uint32_t(bq_quant<FP8>(total[j], multiplier)) |
-                          (uint32_t(bq_quant<FP8>(total[j + 1], multiplier)) << 8) |
-                          (uint32_t(bq_quant<FP8>(total[j + 2], multiplier)) << 16) |
-                          (uint32_t(bq_quant<FP8>(total[j + 3], multiplier)) << 24);
+      for (int c16 = 0; c16 < Q / 16; ++c16) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          uint32_t word = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = c16 * 16 + k4 * 4 + e;
+            const uint32_t qv = bq_quant<FP8>(vals[j], multiplier);
+            word |= qv << (8 * e);
+            if (!diag_tile) {
+              tdst[(size_t(t.b) * trows + (t.col0 + j)) * tld + t.row] = uint8_t(qv);
+            } else if (j <= t.r) {
+              // a diagonal tile stores its lower half and mirrors it
+              out[(size_t(t.b) * g.m + t.row) * g.n + t.col0 + j] = uint8_t(qv);
+              out[(size_t(t.b) * g.m + t.col0 + j) * g.n + t.row] = uint8_t(qv);
+            }
+          }
+          w[k4] = word;
         }
-        uint4* dst = reinterpret_cast<uint4*>(out + (size_t(t.b) * g.m + t.row) * g.n + t.col0);
-#pragma unroll
-        for (int i = 0; i < Q / 16; ++i)
-          dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-        // transpose (update) or mirror (gram / poly off-diagonal tile)
-        uint8_t* tdst = (MODE == BQ_UPDATE) ? static_cast<uint8_t*>(a.out_t) : out;
-        const int trows = (MODE == BQ_UPDATE) ? g.n : g.m;
-        const int tld = (MODE == BQ_UPDATE) ? g.m : g.n;
-#pragma unroll
-        for (int j = 0; j < Q; ++j) {
-          const uint8_t qv = uint8_t(packed[j / 4] >> (8 * (j & 3)));
-          tdst[(size_t(t.b) * trows + (t.col0 + j)) * tld + t.row] = qv;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < Q; ++j) {
-          if (j > t.r) continue;
-          const uint8_t qv = bq_quant<FP8>(total[j], multiplier);
-          out[(size_t(t.b) * g.m + t.row) * g.n + t.col0 + j] = qv;
-          out[(size_t(t.b) * g.m + t.col0 + j) * g.n + t.row] = qv;
-        }
+        if (!diag_tile) dst[c16] = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
   }

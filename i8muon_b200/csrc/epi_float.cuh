@@ -87,6 +87,8 @@ struct EpiFloat {
   // measured bias of a whole-K Gram diagonal is about -1e-8 * K relative, which at
   // K = 4096 alone would exceed the 1e-5 bar of this path.
   static constexpr int PROMOTE_KB = IS_F32 ? 1 : 0;
+  static constexpr int NBUF = IS_F32 ? 2 : 1;
+  static constexpr bool PRESET = false;
   static constexpr int STAGES = 3;
   static constexpr int MIN_CTAS = IS_F32 ? 1 : 2;
   static constexpr uint32_t FMT = IS_F32 ? 2u : (std::is_same<E, __nv_bfloat16>::value ? 1u : 0u);

@@ -57,12 +57,13 @@ struct GemmGeom {
 struct Ctrl {
   unsigned long long full[8];
   unsigned long long empty[8];
-  unsigned long long acc_full[2];
-  unsigned long long acc_empty[2];
+  unsigned long long acc_full[4];
+  unsigned long long acc_empty[4];
   uint32_t tmem_base;
   uint32_t abort;
   float red[8];
   int redi[8];
+  float diag[TILE];
 };
 
 struct TileCtx {
@@ -137,15 +138,15 @@ __device__ inline uint32_t simt_dot(const GemmGeom& g, int b, int row, int col, 
 
 // ------------------------------------------------------------ accumulators
 // Whole-K accumulator: chunk c = columns [32c, 32c+32) of this thread's row.
-template <int KIND, typename Elem>
+template <int KIND, typename Elem, bool DEBUG>
 struct AccWholeK {
   static constexpr bool IN_REGS = false;
   const GemmGeom& g;
   const TileCtx& t;
   uint32_t taddr;  // TMEM address of (lane quarter base, column 0)
   __device__ __forceinline__ void load(int c, uint32_t (&v)[32]) const {
-    if (g.debug_simt) {
-#pragma unroll 1
+    if constexpr (DEBUG) {
+#pragma unroll
       for (int j = 0; j < 32; ++j)
         v[j] = simt_dot<KIND, Elem>(g, t.b, t.row, t.col0 + c * 32 + j, 0, g.k);
     } else {
@@ -176,7 +177,10 @@ struct AccRegs {
 //   the block-scaled promotion of run_blockq), STAGES, MIN_CTAS, IDESC, struct Args,
 //   static __device__ void run(g, args, t, acc)              (whole-K)
 //   static __device__ void run_blockq(g, args, t, tmem, ctrl) (per-K-block)
-template <class Epi>
+// DEBUG = true is the test-only core: no TMA / tcgen05, the epilogue threads compute
+// plain dot products.  It is a separate instantiation so that the product kernels
+// carry none of its code or register pressure.
+template <class Epi, bool DEBUG>
 __global__ void __launch_bounds__(GEMM_THREADS, Epi::MIN_CTAS)
 ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
@@ -185,7 +189,9 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr int PARTS = Epi::PARTS;
   constexpr int STAGE_BYTES = 2 * PARTS * TILE_BYTES;
   constexpr int PROMOTE = Epi::PROMOTE_KB;
-  constexpr int TMEM_COLS = PROMOTE > 0 ? 256 : 128;
+  constexpr int NBUF = Epi::NBUF;          // TMEM accumulators of 128 columns
+  constexpr int TMEM_COLS = 128 * NBUF;
+  static_assert(NBUF == 1 || NBUF == 2 || NBUF == 4, "TMEM allocations are powers of two");
   constexpr int BKE = 128 / int(sizeof(typename Epi::Elem));  // elements per 128-byte K block
 
   extern __shared__ uint8_t smem_raw[];
@@ -203,7 +209,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(smem_u32(&ctrl->full[s]), 1);
       mbar_init(smem_u32(&ctrl->empty[s]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&ctrl->acc_full[i]), 1);
       mbar_init(smem_u32(&ctrl->acc_empty[i]), 128);
     }
@@ -223,7 +229,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   volatile uint32_t* abort_flag = &ctrl->abort;
   const uint32_t smem_base = smem_u32(smem);
 
-  if (!g.debug_simt && warp == 0 && lane == 0) {
+  if (!DEBUG && warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer
     int issued = 0;
     bool ok = true;
@@ -255,7 +261,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
-  } else if (!g.debug_simt && warp == 1 && lane == 0) {
+  } else if (!DEBUG && warp == 1 && lane == 0) {
     // ---------------------------------------------------------- MMA issuer
     bool ok = true;
     for (int kb = 0; kb < g.num_kb; ++kb) {
@@ -267,11 +273,19 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int buf = 0;
       if constexpr (PROMOTE > 0) {
         const int chunk = kb / PROMOTE;
-        buf = chunk & 1;
+        buf = chunk % NBUF;
+        const int use = chunk / NBUF;  // how often this buffer has been filled before
         chunk_first = (kb % PROMOTE) == 0;
         chunk_last = (kb % PROMOTE) == PROMOTE - 1 || kb == g.num_kb - 1;
-        if (chunk_first && chunk >= 2) {
-          ok = mbar_wait(smem_u32(&ctrl->acc_empty[buf]), uint32_t((chunk >> 1) - 1) & 1u, abort_flag);
+        if (chunk_first) {
+          // PRESET: the epilogue warps hand over every buffer filled with the bias
+          // constant (completion 0 is the initial fill); otherwise a buffer is free
+          // until its first reuse.
+          if (Epi::PRESET) {
+            ok = mbar_wait(smem_u32(&ctrl->acc_empty[buf]), uint32_t(use) & 1u, abort_flag);
+          } else if (use >= 1) {
+            ok = mbar_wait(smem_u32(&ctrl->acc_empty[buf]), uint32_t(use - 1) & 1u, abort_flag);
+          }
           if (!ok) break;
         }
         d = tmem_base + uint32_t(buf * TILE);
@@ -286,7 +300,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // 32 bytes of K per instruction: advance the start address inside the
         // 128-byte swizzle row (address field is in 16-byte units).
         const uint64_t adv = uint64_t(ks * 2);
-        uint32_t accumulate = (chunk_first && ks == 0) ? 0u : 1u;
+        uint32_t accumulate = (!Epi::PRESET && chunk_first && ks == 0) ? 0u : 1u;
         umma<Epi::KIND>(d, adesc + adv, bdesc + adv, Epi::IDESC, accumulate);
         if constexpr (PARTS == 2) {
           // split-TF32: hi*hi (above) + hi*lo + lo*hi
@@ -318,10 +332,10 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     t.ctrl = ctrl;
     const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16);
     if constexpr (Epi::BLOCKQ) {
-      Epi::run_blockq(g, args, t, taddr, abort_flag);
+      Epi::template run_blockq<DEBUG>(g, args, t, taddr, abort_flag);
     } else if constexpr (PROMOTE > 0) {
-      if (g.debug_simt) {
-        AccWholeK<Epi::KIND, typename Epi::Elem> acc{g, t, taddr};
+      if constexpr (DEBUG) {
+        AccWholeK<Epi::KIND, typename Epi::Elem, true> acc{g, t, taddr};
         Epi::run(g, args, t, acc);
       } else {
         // Chunked promotion: the tensor core accumulates with truncation, so a
@@ -334,8 +348,8 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
 #pragma unroll 1
         for (int c = 0; c < chunks; ++c) {
-          const int buf = c & 1;
-          ok = mbar_wait(smem_u32(&ctrl->acc_full[buf]), uint32_t(c >> 1) & 1u, abort_flag);
+          const int buf = c % NBUF;
+          ok = mbar_wait(smem_u32(&ctrl->acc_full[buf]), uint32_t(c / NBUF) & 1u, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
@@ -359,13 +373,13 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     } else {
       bool ok = true;
-      if (!g.debug_simt) {
+      if constexpr (!DEBUG) {
         ok = mbar_wait(smem_u32(&ctrl->acc_full[0]), 0u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);  // keep the warp together for tcgen05.ld
         tc_fence_after();
       }
       if (ok) {
-        AccWholeK<Epi::KIND, typename Epi::Elem> acc{g, t, taddr};
+        AccWholeK<Epi::KIND, typename Epi::Elem, DEBUG> acc{g, t, taddr};
         Epi::run(g, args, t, acc);
       } else if (lane == 0) {
         atomicCAS(g.status, 0u, unsigned(ST_EPILOGUE_TIMEOUT) | unsigned(blockIdx.x & 0xff));
