@@ -92,6 +92,11 @@ struct EpiBq {
   static constexpr bool PRESET = !FP8;     // INT8: accumulators start at the bias constant
   static constexpr int STAGES = 4;
   static constexpr int MIN_CTAS = 1;
+  // eight epilogue warps: two per scheduler, each thread owns half a row (64 columns),
+  // so one warp's TMEM-load latency hides behind the other's arithmetic
+  static constexpr int EPI_WARPS = 8;
+  static constexpr int CPT = TILE / (EPI_WARPS / 4);   // columns per thread
+  static constexpr int EPI_THREADS = 32 * EPI_WARPS;
   static constexpr uint32_t IDESC =
       FP8 ? make_idesc(1u, 0u, 0u, TILE, TILE) : make_idesc(2u, 1u, 1u, TILE, TILE);
   using Args = BqArgs;
@@ -114,9 +119,10 @@ struct EpiBq {
                                                     volatile uint32_t* abort_flag) {
     constexpr int Q = TILE;
     const int mq = g.m / Q, nq = g.n / Q, kq = g.k / Q;
-    unsigned long long tot[Q / 2];
+    const int c0 = t.half * CPT;  // first tile column of this thread
+    unsigned long long tot[CPT / 2];
 #pragma unroll
-    for (int j = 0; j < Q / 2; ++j) tot[j] = 0ull;
+    for (int j = 0; j < CPT / 2; ++j) tot[j] = 0ull;
     bool ok = true;
     if constexpr (DEBUG) {
       // debug core: plain dot products per K block, same promotion arithmetic
@@ -124,9 +130,9 @@ struct EpiBq {
       for (int kb = 0; kb < g.num_kb; ++kb) {
         const float s = block_scale(g, a, t, kb, mq, nq, kq);
 #pragma unroll 4
-        for (int j = 0; j < Q / 2; ++j) {
-          uint32_t v0 = simt_dot<KIND, uint8_t>(g, t.b, t.row, t.col0 + 2 * j, kb * Q, kb * Q + Q);
-          uint32_t v1 = simt_dot<KIND, uint8_t>(g, t.b, t.row, t.col0 + 2 * j + 1, kb * Q, kb * Q + Q);
+        for (int j = 0; j < CPT / 2; ++j) {
+          uint32_t v0 = simt_dot<KIND, uint8_t>(g, t.b, t.row, t.col0 + c0 + 2 * j, kb * Q, kb * Q + Q);
+          uint32_t v1 = simt_dot<KIND, uint8_t>(g, t.b, t.row, t.col0 + c0 + 2 * j + 1, kb * Q, kb * Q + Q);
           float p0 = FP8 ? __uint_as_float(v0) : float(int(v0));
           float p1 = FP8 ? __uint_as_float(v1) : float(int(v1));
           tot[j] = pack2(__float_as_uint(__fmaf_rn(p0, s, lane0(tot[j]))),
@@ -137,7 +143,10 @@ struct EpiBq {
       if constexpr (PRESET) {
         // fill every accumulator with the bias constant, then hand them to the MMA warp
 #pragma unroll
-        for (int c = 0; c < NBUF * Q / 32; ++c) tmem_st32_fill(taddr + uint32_t(c * 32), I8_MAGIC_BITS);
+        for (int i = 0; i < NBUF; ++i)
+#pragma unroll
+          for (int c = 0; c < CPT / 32; ++c)
+            tmem_st32_fill(taddr + uint32_t(i * Q + c0 + c * 32), I8_MAGIC_BITS);
         tmem_wait_st();
         tc_fence_before();
 #pragma unroll
@@ -154,15 +163,21 @@ struct EpiBq {
         if (!ok) break;
         tc_fence_after();
         const bool refill = PRESET && (kb + NBUF < g.num_kb);
+        // both 32-column loads of this thread's slice are in flight before the first wait
+        uint32_t v[CPT / 32][32];
 #pragma unroll
-        for (int c = 0; c < Q / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld32(taddr + uint32_t(buf * Q + c * 32), v);
-          tmem_wait_ld();
-          if (refill) tmem_st32_fill(taddr + uint32_t(buf * Q + c * 32), I8_MAGIC_BITS);
+        for (int c = 0; c < CPT / 32; ++c) tmem_ld32(taddr + uint32_t(buf * Q + c0 + c * 32), v[c]);
+        tmem_wait_ld();
+        if (refill) {
+#pragma unroll
+          for (int c = 0; c < CPT / 32; ++c)
+            tmem_st32_fill(taddr + uint32_t(buf * Q + c0 + c * 32), I8_MAGIC_BITS);
+        }
+#pragma unroll
+        for (int c = 0; c < CPT / 32; ++c) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            unsigned long long p = pack2(v[2 * j], v[2 * j + 1]);
+            unsigned long long p = pack2(v[c][2 * j], v[c][2 * j + 1]);
             if constexpr (PRESET) p = add2(p, neg_magic);  // exact: float(partial)
             tot[c * 16 + j] = fma2(p, s2, tot[c * 16 + j]);
           }
@@ -174,26 +189,27 @@ struct EpiBq {
       if (!ok && t.lane == 0)
         atomicCAS(g.status, 0u, unsigned(ST_EPILOGUE_TIMEOUT) | unsigned(blockIdx.x & 0xff));
     }
-    float vals[Q];
+    float vals[CPT];
 #pragma unroll
-    for (int j = 0; j < Q / 2; ++j) { vals[2 * j] = lane0(tot[j]); vals[2 * j + 1] = lane1(tot[j]); }
+    for (int j = 0; j < CPT / 2; ++j) { vals[2 * j] = lane0(tot[j]); vals[2 * j + 1] = lane1(tot[j]); }
     // A warp that gave up still walks through the tail's barriers, without storing.
     tail(g, a, t, vals, ok, mq, nq, kq);
   }
 
   // ---------------------------------------------------------------- tile tail
   static __device__ __forceinline__ void tail(const GemmGeom& g, const Args& a, const TileCtx& t,
-                                              float (&vals)[TILE], const bool live, int mq, int nq,
+                                              float (&vals)[CPT], const bool live, int mq, int nq,
                                               int kq) {
-    constexpr int Q = TILE;
+    const int c0 = t.half * CPT;           // first tile column of this thread
+    const int colbase = t.col0 + c0;       // first global column of this thread
     const bool in_rows = t.row < g.lm;
     float drow = 0.f, stile = 0.f;
     if constexpr (MODE != BQ_GRAM) drow = a.da[size_t(t.b) * g.m + t.row];
     if constexpr (MODE == BQ_POLY) {
       stile = a.sa[(size_t(t.b) * mq + t.tm) * kq + t.tn];
       // the column diagonals of this tile, shared through shared memory
-      t.ctrl->diag[t.r] = a.da[size_t(t.b) * g.m + t.col0 + t.r];
-      named_bar_sync(1, 128);
+      if (t.half == 0) t.ctrl->diag[t.r] = a.da[size_t(t.b) * g.m + t.col0 + t.r];
+      named_bar_sync(1, EPI_THREADS);
     }
     if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
       stile = a.sb[(size_t(t.b) * kq + t.tm) * nq + t.tn];
@@ -201,13 +217,13 @@ struct EpiBq {
     const uint4* comp = nullptr;
     if constexpr (MODE == BQ_POLY)
       comp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(g.a_raw) +
-                                            (size_t(t.b) * g.m + t.row) * g.k + t.col0);
+                                            (size_t(t.b) * g.m + t.row) * g.k + colbase);
     if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
-      comp = reinterpret_cast<const uint4*>(a.row_b + (size_t(t.b) * g.m + t.row) * g.n + t.col0);
+      comp = reinterpret_cast<const uint4*>(a.row_b + (size_t(t.b) * g.m + t.row) * g.n + colbase);
 
     float mx = 1e-8f;
 #pragma unroll
-    for (int c16 = 0; c16 < Q / 16; ++c16) {
+    for (int c16 = 0; c16 < CPT / 16; ++c16) {
       uint32_t words[4] = {0u, 0u, 0u, 0u};
       if constexpr (MODE != BQ_GRAM) {
         const uint4 w = comp[c16];
@@ -216,7 +232,7 @@ struct EpiBq {
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
         const int j = c16 * 16 + jj;
-        const int col = t.col0 + j;
+        const int col = colbase + j;
         float val = vals[j];
         if constexpr (MODE == BQ_GRAM) {
           if (col == t.row) {
@@ -227,7 +243,7 @@ struct EpiBq {
           const uint8_t q = uint8_t(words[jj >> 2] >> (8 * (jj & 3)));
           if constexpr (MODE == BQ_POLY) {
             const float v = __fmul_rn(bq_decode<FP8>(q), stile);
-            const float dcol = t.ctrl->diag[j];
+            const float dcol = t.ctrl->diag[c0 + j];
             val = __fadd_rn(val, __fmul_rn(__fadd_rn(drow, dcol), v));
             val = __fmul_rn(val, a.cc);
             val = __fadd_rn(val, __fmul_rn(v, a.cb));
@@ -249,14 +265,14 @@ struct EpiBq {
 
     if constexpr (MODE == BQ_UPDATE_FINAL) {
       if (!live || !in_rows) return;
-      const size_t rbase = (size_t(t.b) * g.lm + t.row) * g.ln + t.col0;
-      const bool wide16 = !a.transpose && a.out_dtype != DT_F32 && (g.ln % 8) == 0 && t.col0 + Q <= g.ln &&
+      const size_t rbase = (size_t(t.b) * g.lm + t.row) * g.ln + colbase;
+      const bool wide16 = !a.transpose && a.out_dtype != DT_F32 && (g.ln % 8) == 0 && colbase + CPT <= g.ln &&
                           (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
       if (wide16) {
-        // this thread's 128 consecutive 16-bit outputs as sixteen 16-byte stores
+        // this thread's consecutive 16-bit outputs as 16-byte stores
         uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + rbase);
 #pragma unroll
-        for (int c8 = 0; c8 < Q / 8; ++c8) {
+        for (int c8 = 0; c8 < CPT / 8; ++c8) {
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -274,8 +290,8 @@ struct EpiBq {
         return;
       }
 #pragma unroll
-      for (int j = 0; j < Q; ++j) {
-        const int col = t.col0 + j;
+      for (int j = 0; j < CPT; ++j) {
+        const int col = colbase + j;
         if (col < g.ln) {
           size_t idx = a.transpose ? (size_t(t.b) * g.ln + col) * g.lm + t.row : rbase + j;
           store_user(a.out, a.out_dtype, idx, vals[j]);
@@ -284,13 +300,14 @@ struct EpiBq {
       return;
     } else {
       mx = warp_max(mx);
-      if (t.lane == 0) t.ctrl->red[t.q] = mx;
-      named_bar_sync(1, 128);
+      if (t.lane == 0) t.ctrl->red[t.ew] = mx;
+      named_bar_sync(1, EPI_THREADS);
       if (!live) return;
-      mx = fmaxf(fmaxf(t.ctrl->red[0], t.ctrl->red[1]), fmaxf(t.ctrl->red[2], t.ctrl->red[3]));
+#pragma unroll
+      for (int i = 0; i < EPI_WARPS; ++i) mx = fmaxf(mx, t.ctrl->red[i]);
       const float multiplier = QMAX / mx;
       const float scale = 1.f / multiplier;
-      if (t.r == 0) {
+      if (t.r == 0 && t.half == 0) {
         a.so[(size_t(t.b) * mq + t.tm) * nq + t.tn] = scale;
         if constexpr (MODE != BQ_UPDATE) a.so[(size_t(t.b) * mq + t.tn) * nq + t.tm] = scale;
       }
@@ -300,9 +317,9 @@ struct EpiBq {
       uint8_t* tdst = (MODE == BQ_UPDATE) ? static_cast<uint8_t*>(a.out_t) : out;
       const int trows = (MODE == BQ_UPDATE) ? g.n : g.m;
       const int tld = (MODE == BQ_UPDATE) ? g.m : g.n;
-      uint4* dst = reinterpret_cast<uint4*>(out + (size_t(t.b) * g.m + t.row) * g.n + t.col0);
+      uint4* dst = reinterpret_cast<uint4*>(out + (size_t(t.b) * g.m + t.row) * g.n + colbase);
 #pragma unroll
-      for (int c16 = 0; c16 < Q / 16; ++c16) {
+      for (int c16 = 0; c16 < CPT / 16; ++c16) {
         uint32_t w[4];
 #pragma unroll
         for (int k4 = 0; k4 < 4; ++k4) {
@@ -313,11 +330,11 @@ struct EpiBq {
             const uint32_t qv = bq_quant<FP8>(vals[j], multiplier);
             word |= qv << (8 * e);
             if (!diag_tile) {
-              tdst[(size_t(t.b) * trows + (t.col0 + j)) * tld + t.row] = uint8_t(qv);
-            } else if (j <= t.r) {
+              tdst[(size_t(t.b) * trows + (colbase + j)) * tld + t.row] = uint8_t(qv);
+            } else if (c0 + j <= t.r) {
               // a diagonal tile stores its lower half and mirrors it
-              out[(size_t(t.b) * g.m + t.row) * g.n + t.col0 + j] = uint8_t(qv);
-              out[(size_t(t.b) * g.m + t.col0 + j) * g.n + t.row] = uint8_t(qv);
+              out[(size_t(t.b) * g.m + t.row) * g.n + colbase + j] = uint8_t(qv);
+              out[(size_t(t.b) * g.m + colbase + j) * g.n + t.row] = uint8_t(qv);
             }
           }
           w[k4] = word;

@@ -89,6 +89,7 @@ struct EpiFloat {
   static constexpr int PROMOTE_KB = IS_F32 ? 1 : 0;
   static constexpr int NBUF = IS_F32 ? 2 : 1;
   static constexpr bool PRESET = false;
+  static constexpr int EPI_WARPS = 4;
   static constexpr int STAGES = 3;
   static constexpr int MIN_CTAS = IS_F32 ? 1 : 2;
   static constexpr uint32_t FMT = IS_F32 ? 2u : (std::is_same<E, __nv_bfloat16>::value ? 1u : 0u);

@@ -37,6 +37,7 @@ struct EpiI8 {
   static constexpr int PROMOTE_KB = 0;
   static constexpr int NBUF = 1;
   static constexpr bool PRESET = false;
+  static constexpr int EPI_WARPS = 4;
   static constexpr int STAGES = 3;
   static constexpr int MIN_CTAS = 2;
   static constexpr uint32_t IDESC = make_idesc(2u, 1u, 1u, TILE, TILE);  // s32 <- s8 * s8

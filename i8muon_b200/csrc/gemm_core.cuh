@@ -30,7 +30,7 @@ namespace i8m {
 
 constexpr int TILE = 128;            // CTA tile is TILE x TILE
 constexpr int TILE_BYTES = TILE * 128;  // one operand tile of one stage (128 rows x 128 B)
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 192;  // default: 2 control warps + 4 epilogue warps
 
 // Error codes written to the status word (first error wins).
 enum StatusCode : unsigned {
@@ -71,6 +71,8 @@ struct TileCtx {
   int r;        // row inside the tile owned by this epilogue thread
   int row;      // global row
   int q;        // TMEM lane quarter of this warp
+  int half;     // column slice of this warp when a row is split over several warps
+  int ew;       // epilogue warp index (0 .. EPI_WARPS-1)
   int lane;
   Ctrl* ctrl;
 };
@@ -180,8 +182,20 @@ struct AccRegs {
 // DEBUG = true is the test-only core: no TMA / tcgen05, the epilogue threads compute
 // plain dot products.  It is a separate instantiation so that the product kernels
 // carry none of its code or register pressure.
+// Warp layout: warp 0 producer, warp 1 MMA issuer.  With four epilogue warps they are
+// warps 2..5.  With eight, the CTA is three warpgroups: warps 0..3 are the control
+// warpgroup (two of them idle) and shrink their register allotment, warps 4..11 are two
+// epilogue warpgroups that grow theirs (setmaxnreg), so that each epilogue thread can
+// hold its slice of the accumulator plus a full set of TMEM loads in flight.
+template <class Epi>
+struct WarpLayout {
+  static constexpr int EPI_WARP0 = Epi::EPI_WARPS == 8 ? 4 : 2;
+  static constexpr int THREADS = 32 * (EPI_WARP0 + Epi::EPI_WARPS);
+  static constexpr bool REBALANCE = Epi::EPI_WARPS == 8;
+};
+
 template <class Epi, bool DEBUG>
-__global__ void __launch_bounds__(GEMM_THREADS, Epi::MIN_CTAS)
+__global__ void __launch_bounds__(WarpLayout<Epi>::THREADS, Epi::MIN_CTAS)
 ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
                GemmGeom g, typename Epi::Args args) {
@@ -211,7 +225,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&ctrl->acc_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty[i]), 128);
+      mbar_init(smem_u32(&ctrl->acc_empty[i]), 32 * Epi::EPI_WARPS);
     }
     ctrl->abort = 0;
     fence_mbar_init();
@@ -228,7 +242,10 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tmem_base = ctrl->tmem_base;
   volatile uint32_t* abort_flag = &ctrl->abort;
   const uint32_t smem_base = smem_u32(smem);
+  constexpr int EPI_WARP0 = WarpLayout<Epi>::EPI_WARP0;
 
+  if (warp < EPI_WARP0) {
+  if constexpr (WarpLayout<Epi>::REBALANCE) setmaxnreg_dec<56>();
   if (!DEBUG && warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer
     int issued = 0;
@@ -322,11 +339,14 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (ok) umma_commit(smem_u32(&ctrl->acc_full[0]));
     }
     if (!ok) atomicCAS(g.status, 0u, unsigned(ST_MMA_TIMEOUT) | unsigned(blockIdx.x & 0xff));
-  } else if (warp >= 2) {
+  }
+  } else {
     // ------------------------------------------------------------ epilogue
+    if constexpr (WarpLayout<Epi>::REBALANCE) setmaxnreg_inc<224>();
     TileCtx t;
     t.b = b; t.tm = tm; t.tn = tn; t.row0 = row0; t.col0 = col0;
     t.q = warp & 3; t.lane = lane;
+    t.ew = warp - EPI_WARP0; t.half = (warp - EPI_WARP0) >> 2;
     t.r = t.q * 32 + lane;
     t.row = row0 + t.r;
     t.ctrl = ctrl;

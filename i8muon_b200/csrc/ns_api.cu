@@ -125,7 +125,7 @@ int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_
   }
   auto kernel = g_debug_simt ? ns_gemm_kernel<Epi, true> : ns_gemm_kernel<Epi, false>;
   CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
-  kernel<<<dim3(unsigned(blocks)), GEMM_THREADS, SMEM, stream>>>(ma, mb, ma2, mb2, g, args);
+  kernel<<<dim3(unsigned(blocks)), WarpLayout<Epi>::THREADS, SMEM, stream>>>(ma, mb, ma2, mb2, g, args);
   LAUNCH_CHECK(name);
   return 0;
 }
