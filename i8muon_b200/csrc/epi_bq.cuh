@@ -113,6 +113,36 @@ struct EpiBq {
     return __fmul_rn(a.sa[(size_t(t.b) * mq + t.tm) * kq + kb], bs);
   }
 
+  // Fold one K block (this thread's 64 partials) into the FP32 totals:
+  //   total = fmaf(float(partial), s, total)
+  // INT8 partials arrive biased by 12582912 (preset accumulator); one exact subtraction
+  // recovers float(partial).  Packed flavour: two IEEE operations per instruction.
+  static __device__ __forceinline__ void fold64p(unsigned long long (&tot)[32], const uint32_t (&v)[2][32],
+                                                 const float s) {
+    const unsigned long long neg_magic = pack2(__float_as_uint(-I8_MAGIC), __float_as_uint(-I8_MAGIC));
+    const unsigned long long s2 = pack2(__float_as_uint(s), __float_as_uint(s));
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        unsigned long long p = pack2(v[c][2 * j], v[c][2 * j + 1]);
+        if constexpr (PRESET) p = add2(p, neg_magic);
+        tot[c * 16 + j] = fma2(p, s2, tot[c * 16 + j]);
+      }
+    }
+  }
+  static __device__ __forceinline__ void fold64(float (&tot)[64], const uint32_t (&v)[2][32], const float s) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float p = __uint_as_float(v[c][j]);
+        if constexpr (PRESET) p = __fadd_rn(p, -I8_MAGIC);
+        tot[c * 32 + j] = __fmaf_rn(p, s, tot[c * 32 + j]);
+      }
+    }
+  }
+
   template <bool DEBUG>
   static __device__ __forceinline__ void run_blockq(const GemmGeom& g, const Args& a,
                                                     const TileCtx& t, uint32_t taddr,
@@ -149,8 +179,9 @@ struct EpiBq {
             tmem_st32_fill(taddr + uint32_t(i * Q + c0 + c * 32), I8_MAGIC_BITS);
         tmem_wait_st();
         tc_fence_before();
-#pragma unroll
-        for (int i = 0; i < NBUF; ++i) mbar_arrive(smem_u32(&t.ctrl->acc_empty[i]));
+        __syncwarp();
+        if (t.lane == 0)
+          for (int i = 0; i < NBUF; ++i) mbar_arrive(smem_u32(&t.ctrl->acc_empty[i]));
       }
       const unsigned long long neg_magic = pack2(__float_as_uint(-I8_MAGIC), __float_as_uint(-I8_MAGIC));
 #pragma unroll 1
@@ -184,7 +215,8 @@ struct EpiBq {
         }
         if (refill) tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(smem_u32(&t.ctrl->acc_empty[buf]));
+        __syncwarp();
+        if (t.lane == 0) mbar_arrive(smem_u32(&t.ctrl->acc_empty[buf]));
       }
       if (!ok && t.lane == 0)
         atomicCAS(g.status, 0u, unsigned(ST_EPILOGUE_TIMEOUT) | unsigned(blockIdx.x & 0xff));
@@ -208,7 +240,7 @@ struct EpiBq {
     if constexpr (MODE == BQ_POLY) {
       stile = a.sa[(size_t(t.b) * mq + t.tm) * kq + t.tn];
       // the column diagonals of this tile, shared through shared memory
-      if (t.half == 0) t.ctrl->diag[t.r] = a.da[size_t(t.b) * g.m + t.col0 + t.r];
+      if (t.half == 0) t.diag[t.r] = a.da[size_t(t.b) * g.m + t.col0 + t.r];
       named_bar_sync(1, EPI_THREADS);
     }
     if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
@@ -226,7 +258,11 @@ struct EpiBq {
     for (int c16 = 0; c16 < CPT / 16; ++c16) {
       uint32_t words[4] = {0u, 0u, 0u, 0u};
       if constexpr (MODE != BQ_GRAM) {
+#ifndef I8M_EXP_NO_COMP
         const uint4 w = comp[c16];
+#else
+        const uint4 w = make_uint4(0x01020304u + c16, 0x05060708u, 0x090a0b0cu, 0x0d0e0f10u);
+#endif
         words[0] = w.x; words[1] = w.y; words[2] = w.z; words[3] = w.w;
       }
 #pragma unroll
@@ -243,7 +279,7 @@ struct EpiBq {
           const uint8_t q = uint8_t(words[jj >> 2] >> (8 * (jj & 3)));
           if constexpr (MODE == BQ_POLY) {
             const float v = __fmul_rn(bq_decode<FP8>(q), stile);
-            const float dcol = t.ctrl->diag[c0 + j];
+            const float dcol = t.diag[c0 + j];
             val = __fadd_rn(val, __fmul_rn(__fadd_rn(drow, dcol), v));
             val = __fmul_rn(val, a.cc);
             val = __fadd_rn(val, __fmul_rn(v, a.cb));
@@ -300,11 +336,11 @@ struct EpiBq {
       return;
     } else {
       mx = warp_max(mx);
-      if (t.lane == 0) t.ctrl->red[t.ew] = mx;
+      if (t.lane == 0) t.red[t.ew] = mx;
       named_bar_sync(1, EPI_THREADS);
       if (!live) return;
 #pragma unroll
-      for (int i = 0; i < EPI_WARPS; ++i) mx = fmaxf(mx, t.ctrl->red[i]);
+      for (int i = 0; i < EPI_WARPS; ++i) mx = fmaxf(mx, t.red[i]);
       const float multiplier = QMAX / mx;
       const float scale = 1.f / multiplier;
       if (t.r == 0 && t.half == 0) {
@@ -330,7 +366,9 @@ struct EpiBq {
             const uint32_t qv = bq_quant<FP8>(vals[j], multiplier);
             word |= qv << (8 * e);
             if (!diag_tile) {
+#ifndef I8M_EXP_NO_TSTORE
               tdst[(size_t(t.b) * trows + (colbase + j)) * tld + t.row] = uint8_t(qv);
+#endif
             } else if (c0 + j <= t.r) {
               // a diagonal tile stores its lower half and mirrors it
               out[(size_t(t.b) * g.m + t.row) * g.n + colbase + j] = uint8_t(qv);
@@ -339,7 +377,11 @@ struct EpiBq {
           }
           w[k4] = word;
         }
+#ifndef I8M_EXP_NO_RSTORE
         if (!diag_tile) dst[c16] = make_uint4(w[0], w[1], w[2], w[3]);
+#else
+        if (w[0] == 0x12345678u && w[1] == 77u) dst[c16] = make_uint4(w[0], w[1], w[2], w[3]);
+#endif
       }
     }
   }

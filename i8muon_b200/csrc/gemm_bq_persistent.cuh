@@ -1,0 +1,248 @@
+// Persistent kernel for the 128x128 block-quantised GEMMs (the dominant kernels of
+// the INT8-BQ / FP8-BQ Newton-Schulz step).
+//
+// One CTA per SM walks a static round-robin list of output tiles.  Three warpgroups:
+//   warpgroup 0  warps 0 and 2 = TMA producers, warps 1 and 3 = tcgen05.mma issuers;
+//                registers trimmed with setmaxnreg
+//   warpgroups 1-2  eight epilogue warps; thread = one accumulator row x 64 columns
+// The shared-memory ring and the four TMEM accumulators are indexed by a K-block
+// counter that runs across tiles, so the producers and the tensor core move on to the
+// next tile while the epilogue warps still quantise and store the previous one; per
+// tile there is no launch, no barrier initialisation and no TMEM allocation.
+//
+// Measured facts behind the structure (B200, update GEMM 4096 x 14336, K = 4096):
+//   * every K block has its own accumulator, so K blocks are independent work items for
+//     the tensor core.  ONE issuing thread needs ~730 cycles of dependent instructions
+//     per K block (two barrier waits, descriptors, four MMAs, two commits) against 271
+//     cycles of MMA time; two producers and two issuers on alternate K blocks cut the
+//     floor of the pipeline from 0.37 to 0.25 us per K block;
+//   * the per-K-block scale products are staged in shared memory per tile;
+//   * one mbarrier arrival per epilogue warp, not per thread.
+#pragma once
+#include "epi_bq.cuh"
+
+namespace i8m {
+
+constexpr int BQP_STAGES = 6;
+constexpr int BQP_THREADS = 384;
+constexpr int BQP_MAX_KB = 512;  // K blocks whose scales are staged in shared memory (K <= 65536)
+constexpr int BQP_CTRL_REGS = 56;
+constexpr int BQP_EPI_REGS = 224;
+
+template <class Epi>
+__global__ void __launch_bounds__(BQP_THREADS, 1)
+bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     GemmGeom g, typename Epi::Args args) {
+  constexpr int STAGES = BQP_STAGES;
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  constexpr int NBUF = 4;
+  constexpr int Q = TILE;
+  constexpr int CPT = 64;  // columns per epilogue thread
+  static_assert(Epi::CPT == CPT && Epi::EPI_WARPS == 8 && Epi::NBUF == NBUF, "layout mismatch with the epilogue");
+  static_assert(STAGES % 2 == 0, "two producers alternate stages");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * STAGE_BYTES);
+  float* scale_ring = reinterpret_cast<float*>(ctrl + 1);  // [2][BQP_MAX_KB] products sA*sB per K block
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int i = 0; i < NBUF; ++i) {
+      mbar_init(smem_u32(&ctrl->acc_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->acc_empty[i]), 8);  // one arrival per epilogue warp
+    }
+    ctrl->abort = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), 128 * NBUF);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+  volatile uint32_t* abort_flag = &ctrl->abort;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
+  const uint32_t accf0 = smem_u32(&ctrl->acc_full[0]), acce0 = smem_u32(&ctrl->acc_empty[0]);
+
+  const int total_tiles = g.tiles_per_batch * g.batch;
+  const int my_tiles = (total_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+  const int nkb = g.num_kb;
+  const int my_kb = my_tiles * nkb;  // K blocks this CTA pushes through the pipeline
+
+  if (warp < 4) {
+    setmaxnreg_dec<BQP_CTRL_REGS>();
+    const int par = warp >> 1;  // this thread takes K blocks gk = par, par + 2, ...
+    if ((warp & 1) == 0 && lane == 0) {
+      // ------------------------------------------------------------ producer
+      int it = 0, kb = par, b = 0, tm = 0, tn = 0;
+      while (kb >= nkb && it < my_tiles) { kb -= nkb; ++it; }
+      if (it < my_tiles) decode_tile(g, int(blockIdx.x) + it * int(gridDim.x), b, tm, tn);
+      int s = par;              // stage of the current K block, advances by 2 modulo STAGES
+      uint32_t wrap = 0;        // how often this stage has been used before
+      int issued = 0;
+      bool ok = true;
+      for (int gk = par; gk < my_kb; gk += 2) {
+        if (wrap > 0) {
+          ok = mbar_wait(empty0 + 8u * uint32_t(s), (wrap - 1) & 1u, abort_flag);
+          if (!ok) break;
+        }
+        const uint32_t bar = full0 + 8u * uint32_t(s);
+        const uint32_t dst = smem_base + uint32_t(s * STAGE_BYTES);
+        mbar_arrive_expect_tx(bar, STAGE_BYTES);
+        tma_load_3d(dst, &map_a, bar, kb * Q, tm * Q, b);
+        tma_load_3d(dst + TILE_BYTES, &map_b, bar, kb * Q, tn * Q, b);
+        ++issued;
+        s += 2;
+        if (s >= STAGES) { s -= STAGES; ++wrap; }
+        kb += 2;
+        if (kb >= nkb) {
+          do { kb -= nkb; ++it; } while (kb >= nkb && it < my_tiles);
+          if (it < my_tiles) decode_tile(g, int(blockIdx.x) + it * int(gridDim.x), b, tm, tn);
+        }
+      }
+      if (!ok) {
+        atomicCAS(g.status, 0u, unsigned(ST_PRODUCER_TIMEOUT) | unsigned(blockIdx.x & 0xff));
+        // let the copies that were issued land before shared memory is released
+        for (int back = 0; back < STAGES / 2 && back < issued; ++back) {
+          const int n = par + 2 * (issued - 1 - back);     // global K block index
+          const uint32_t parity = uint32_t(n / STAGES) & 1u;
+          for (int spin = 0; spin < (1 << 20) && !mbar_try_wait(full0 + 8u * uint32_t(n % STAGES), parity); ++spin) {
+          }
+        }
+      }
+    } else if ((warp & 1) == 1 && lane == 0) {
+      // ---------------------------------------------------------- MMA issuer
+      int s = par, buf = par;   // both advance by 2 (modulo STAGES / NBUF)
+      uint32_t wrap = 0, use = 0;
+      bool ok = true;
+      for (int gk = par; gk < my_kb; gk += 2) {
+        // PRESET: every use waits for the epilogue's refill (completion 0 = initial fill);
+        // otherwise a buffer is free until its first reuse
+        if (Epi::PRESET) ok = mbar_wait(acce0 + 8u * uint32_t(buf), use & 1u, abort_flag);
+        else if (use >= 1) ok = mbar_wait(acce0 + 8u * uint32_t(buf), (use - 1) & 1u, abort_flag);
+        if (!ok) break;
+        ok = mbar_wait(full0 + 8u * uint32_t(s), wrap & 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d = tmem_base + uint32_t(buf * Q);
+        const uint32_t sa = smem_base + uint32_t(s * STAGE_BYTES);
+        const uint64_t adesc = make_smem_desc_sw128(sa);
+        const uint64_t bdesc = make_smem_desc_sw128(sa + TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint32_t accumulate = (!Epi::PRESET && ks == 0) ? 0u : 1u;
+          umma<Epi::KIND>(d, adesc + uint64_t(ks * 2), bdesc + uint64_t(ks * 2), Epi::IDESC, accumulate);
+        }
+        umma_commit(empty0 + 8u * uint32_t(s));
+        umma_commit(accf0 + 8u * uint32_t(buf));
+        s += 2;
+        if (s >= STAGES) { s -= STAGES; ++wrap; }
+        buf += 2;
+        if (buf >= NBUF) { buf -= NBUF; ++use; }
+      }
+      if (!ok) atomicCAS(g.status, 0u, unsigned(ST_MMA_TIMEOUT) | unsigned(blockIdx.x & 0xff));
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue
+    setmaxnreg_inc<BQP_EPI_REGS>();
+    TileCtx t;
+    t.q = warp & 3; t.lane = lane;
+    t.ew = warp - 4; t.half = (warp - 4) >> 2;
+    t.r = t.q * 32 + lane;
+    t.ctrl = ctrl;
+    t.diag = ctrl->diag;
+    const int c0 = t.half * CPT;
+    const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16) + uint32_t(c0);
+    const int mq = g.m / Q, nq = g.n / Q, kq = g.k / Q;
+    if constexpr (Epi::PRESET) {
+#pragma unroll
+      for (int i = 0; i < NBUF; ++i) {
+        tmem_st32_fill(taddr + uint32_t(i * Q), I8_MAGIC_BITS);
+        tmem_st32_fill(taddr + uint32_t(i * Q + 32), I8_MAGIC_BITS);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        for (int i = 0; i < NBUF; ++i) mbar_arrive(acce0 + 8u * uint32_t(i));
+    }
+    bool ok = true;
+    int buf = 0;
+    uint32_t use = 0;
+    const bool staged = nkb <= BQP_MAX_KB;
+    for (int it = 0; it < my_tiles; ++it) {
+      decode_tile(g, int(blockIdx.x) + it * int(gridDim.x), t.b, t.tm, t.tn);
+      t.row0 = t.tm * Q; t.col0 = t.tn * Q;
+      t.row = t.row0 + t.r;
+      t.red = ctrl->red2[it & 1];
+      // scale products of this tile -> shared memory (a slow warp of tile it-1 cannot still
+      // be reading this half of the ring: it passed this barrier of tile it-1 after that)
+      float* sc = scale_ring + (it & 1) * BQP_MAX_KB;
+      if (staged) {
+        for (int k = int(threadIdx.x) - 128; k < nkb; k += 256) sc[k] = Epi::block_scale(g, args, t, k, mq, nq, kq);
+        named_bar_sync(2, 256);
+      }
+#ifdef I8M_BQ_SCALAR
+      float tot[CPT];
+#pragma unroll
+      for (int j = 0; j < CPT; ++j) tot[j] = 0.f;
+#else
+      unsigned long long tot2[CPT / 2];
+#pragma unroll
+      for (int j = 0; j < CPT / 2; ++j) tot2[j] = 0ull;
+#endif
+      const int gk0 = it * nkb;
+#pragma unroll 1
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const float s = staged ? sc[kb] : Epi::block_scale(g, args, t, kb, mq, nq, kq);
+        ok = mbar_wait(accf0 + 8u * uint32_t(buf), use & 1u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);  // keep the warp together for tcgen05.ld
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t v[2][32];
+        tmem_ld32(taddr + uint32_t(buf * Q), v[0]);
+        tmem_ld32(taddr + uint32_t(buf * Q + 32), v[1]);
+        tmem_wait_ld();
+        const bool refill = Epi::PRESET && (gk0 + kb + NBUF < my_kb);
+        if (refill) {
+          tmem_st32_fill(taddr + uint32_t(buf * Q), I8_MAGIC_BITS);
+          tmem_st32_fill(taddr + uint32_t(buf * Q + 32), I8_MAGIC_BITS);
+        }
+#ifdef I8M_BQ_SCALAR
+        Epi::fold64(tot, v, s);
+#else
+        Epi::fold64p(tot2, v, s);
+#endif
+        if (refill) tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acce0 + 8u * uint32_t(buf));
+        if (++buf == NBUF) { buf = 0; ++use; }
+      }
+      if (!ok && lane == 0)
+        atomicCAS(g.status, 0u, unsigned(ST_EPILOGUE_TIMEOUT) | unsigned(blockIdx.x & 0xff));
+#ifndef I8M_BQ_SCALAR
+      float tot[CPT];
+#pragma unroll
+      for (int j = 0; j < CPT / 2; ++j) { tot[2 * j] = lane0(tot2[j]); tot[2 * j + 1] = lane1(tot2[j]); }
+#endif
+      // a warp that gave up still walks through the tail's barriers, without storing
+      Epi::tail(g, args, t, tot, ok, mq, nq, kq);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 128 * NBUF);
+}
+
+}  // namespace i8m

@@ -64,6 +64,7 @@ struct Ctrl {
   float red[8];
   int redi[8];
   float diag[TILE];
+  float red2[2][8];
 };
 
 struct TileCtx {
@@ -75,6 +76,8 @@ struct TileCtx {
   int ew;       // epilogue warp index (0 .. EPI_WARPS-1)
   int lane;
   Ctrl* ctrl;
+  float* red;   // shared scratch for the tile-wide reduction (one float per epilogue warp)
+  float* diag;  // shared scratch: TILE floats
 };
 
 __device__ __forceinline__ void decode_tile(const GemmGeom& g, int linear, int& b, int& tm,
@@ -225,7 +228,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&ctrl->acc_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->acc_empty[i]), 32 * Epi::EPI_WARPS);
+      mbar_init(smem_u32(&ctrl->acc_empty[i]), Epi::EPI_WARPS);  // one arrival per epilogue warp
     }
     ctrl->abort = 0;
     fence_mbar_init();
@@ -350,6 +353,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     t.r = t.q * 32 + lane;
     t.row = row0 + t.r;
     t.ctrl = ctrl;
+    t.red = ctrl->red; t.diag = ctrl->diag;
     const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16);
     if constexpr (Epi::BLOCKQ) {
       Epi::template run_blockq<DEBUG>(g, args, t, taddr, abort_flag);
@@ -382,7 +386,8 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int j = 0; j < 32; ++j) total[cc * 32 + j] = __fadd_rn(total[cc * 32 + j], __uint_as_float(v[j]));
           }
           tc_fence_before();
-          mbar_arrive(smem_u32(&ctrl->acc_empty[buf]));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctrl->acc_empty[buf]));
         }
         if (ok) {
           AccRegs acc{total};

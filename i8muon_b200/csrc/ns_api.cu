@@ -6,6 +6,7 @@
 #include "epi_bq.cuh"
 #include "epi_float.cuh"
 #include "epi_int8.cuh"
+#include "gemm_bq_persistent.cuh"
 #include "passes.cuh"
 
 #include <cstdarg>
@@ -126,6 +127,51 @@ int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_
   auto kernel = g_debug_simt ? ns_gemm_kernel<Epi, true> : ns_gemm_kernel<Epi, false>;
   CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
   kernel<<<dim3(unsigned(blocks)), WarpLayout<Epi>::THREADS, SMEM, stream>>>(ma, mb, ma2, mb2, g, args);
+  LAUNCH_CHECK(name);
+  return 0;
+}
+
+// Block-quantised GEMMs: persistent kernel, one CTA per SM (the debug core keeps the
+// one-tile-per-CTA skeleton).
+int sm_count() {
+  static int counts[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+  if (counts[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+    counts[device] = n;
+  }
+  return counts[device];
+}
+
+template <class Epi>
+int launch_bq(const void* a, const void* bt, int batch, int m, int n, int k, int lm, int ln, int sym,
+              unsigned* status, const typename Epi::Args& args, cudaStream_t stream, const char* name) {
+  if (g_debug_simt)
+    return launch_gemm<Epi>(a, nullptr, bt, nullptr, batch, m, n, k, lm, ln, sym, status, args, stream, name);
+  if (batch < 1 || m < 1 || n < 1 || k < 1) return fail(I8M_E_ARGUMENT, "%s: empty problem", name);
+  if (!a || !bt || !status) return fail(I8M_E_ARGUMENT, "%s: null operand or status pointer", name);
+  if (sym && m != n) return fail(I8M_E_ARGUMENT, "%s: symmetric product needs m == n", name);
+  constexpr size_t SMEM = size_t(BQP_STAGES) * 2 * TILE_BYTES + sizeof(Ctrl) + 2 * BQP_MAX_KB * sizeof(float) + 1024;
+  GemmGeom g;
+  g.batch = batch; g.m = m; g.n = n; g.k = k; g.lm = lm; g.ln = ln;
+  g.tiles_m = cdiv(m, TILE); g.tiles_n = cdiv(n, TILE);
+  g.sym = sym;
+  g.tiles_per_batch = sym ? g.tiles_m * (g.tiles_m + 1) / 2 : g.tiles_m * g.tiles_n;
+  g.num_kb = cdiv(k, 128);
+  g.debug_simt = 0;
+  g.a_raw = a; g.b_raw = bt; g.status = status;
+  const long long tiles = (long long)g.tiles_per_batch * batch;
+  if (tiles > 0x7fffffffLL / 2) return fail(I8M_E_LIMIT, "%s: too many tiles", name);
+  if ((long long)g.num_kb * ((tiles + 1) / 1) > 0x7fffffffLL) return fail(I8M_E_LIMIT, "%s: too many K blocks", name);
+  CUtensorMap ma, mb;
+  if (int rc = make_operand_map(&ma, a, 1, k, m, batch)) return rc;
+  if (int rc = make_operand_map(&mb, bt, 1, k, n, batch)) return rc;
+  auto kernel = bq_persistent_kernel<Epi>;
+  CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
+  const unsigned grid = unsigned(std::min<long long>(tiles, sm_count()));
+  kernel<<<grid, BQP_THREADS, SMEM, stream>>>(ma, mb, g, args);
   LAUNCH_CHECK(name);
   return 0;
 }
@@ -416,24 +462,21 @@ static int bq_gemm_typed(int mode, const void* a, const float* sa, const float* 
   g.ca = ca; g.cb = cb; g.cc = cc; g.out_dtype = out_dtype; g.transpose = transpose;
   if (mode == 0) {
     if (!so || !dout) return fail(I8M_E_ARGUMENT, "bq_gemm: gram needs scale and diagonal outputs");
-    return launch_gemm<EpiBq<FP8, BQ_GRAM>>(a, nullptr, b_t, nullptr, batch, m, n, k, lm, ln, 1, status,
-                                            g, stream, "bq_gemm(gram)");
+    return launch_bq<EpiBq<FP8, BQ_GRAM>>(a, b_t, batch, m, n, k, lm, ln, 1, status, g, stream, "bq_gemm(gram)");
   }
   if (mode == 1) {
     if (!so || !dout || !da) return fail(I8M_E_ARGUMENT, "bq_gemm: poly needs scale, diagonal in and out");
-    return launch_gemm<EpiBq<FP8, BQ_POLY>>(a, nullptr, b_t, nullptr, batch, m, n, k, lm, ln, 1, status,
-                                            g, stream, "bq_gemm(poly)");
+    return launch_bq<EpiBq<FP8, BQ_POLY>>(a, b_t, batch, m, n, k, lm, ln, 1, status, g, stream, "bq_gemm(poly)");
   }
   if (mode == 2) {
     if (!da || !row_b) return fail(I8M_E_ARGUMENT, "bq_gemm: update needs the diagonal and row_b");
     if (final) {
       if (!float_dtype_ok(out_dtype)) return fail(I8M_E_ARGUMENT, "bq_gemm: bad out_dtype");
-      return launch_gemm<EpiBq<FP8, BQ_UPDATE_FINAL>>(a, nullptr, b_t, nullptr, batch, m, n, k, lm, ln,
-                                                      0, status, g, stream, "bq_gemm(final update)");
+      return launch_bq<EpiBq<FP8, BQ_UPDATE_FINAL>>(a, b_t, batch, m, n, k, lm, ln, 0, status, g, stream,
+                                                   "bq_gemm(final update)");
     }
     if (!so || !out_t) return fail(I8M_E_ARGUMENT, "bq_gemm: update needs scale and transposed outputs");
-    return launch_gemm<EpiBq<FP8, BQ_UPDATE>>(a, nullptr, b_t, nullptr, batch, m, n, k, lm, ln, 0,
-                                              status, g, stream, "bq_gemm(update)");
+    return launch_bq<EpiBq<FP8, BQ_UPDATE>>(a, b_t, batch, m, n, k, lm, ln, 0, status, g, stream, "bq_gemm(update)");
   }
   return fail(I8M_E_ARGUMENT, "bq_gemm: bad mode %d", mode);
 }

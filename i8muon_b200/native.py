@@ -65,11 +65,13 @@ EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 @lru_cache(maxsize=1)
 def library() -> ctypes.CDLL:
     """Load ``libi8muon_b200.so``; raise if it has not been built."""
-    if not LIBRARY.exists():
+    import os
+    path = os.environ.get("I8MUON_B200_LIBRARY", str(LIBRARY))  # explicit path to another build of the same ABI
+    if not os.path.exists(path):
         raise NativeError(
-            f"{LIBRARY} is missing: build it with `python -m i8muon_b200.build` "
+            f"{path} is missing: build it with `python -m i8muon_b200.build` "
             "(there is no fallback path)")
-    lib = ctypes.CDLL(str(LIBRARY))
+    lib = ctypes.CDLL(path)
     for name, (restype, argtypes) in _SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.restype = restype
