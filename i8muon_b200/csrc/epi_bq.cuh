@@ -97,6 +97,8 @@ struct EpiBq {
   static constexpr int EPI_WARPS = 8;
   static constexpr int CPT = TILE / (EPI_WARPS / 4);   // columns per thread
   static constexpr int EPI_THREADS = 32 * EPI_WARPS;
+  static constexpr int TSM_PITCH = TILE + 16;       // row pitch of the transposed staging tile
+  static constexpr int TSM_BYTES = TILE * TSM_PITCH;
   static constexpr uint32_t IDESC =
       FP8 ? make_idesc(1u, 0u, 0u, TILE, TILE) : make_idesc(2u, 1u, 1u, TILE, TILE);
   using Args = BqArgs;
@@ -225,44 +227,57 @@ struct EpiBq {
 #pragma unroll
     for (int j = 0; j < CPT / 2; ++j) { vals[2 * j] = lane0(tot[j]); vals[2 * j + 1] = lane1(tot[j]); }
     // A warp that gave up still walks through the tail's barriers, without storing.
-    tail(g, a, t, vals, ok, mq, nq, kq);
+    const Pre pre = tail_prefetch(g, a, t, mq, nq, kq);
+    tail(g, a, t, vals, ok, pre, mq, nq, kq);
   }
 
-  // ---------------------------------------------------------------- tile tail
-  static __device__ __forceinline__ void tail(const GemmGeom& g, const Args& a, const TileCtx& t,
-                                              float (&vals)[CPT], const bool live, int mq, int nq,
-                                              int kq) {
-    const int c0 = t.half * CPT;           // first tile column of this thread
-    const int colbase = t.col0 + c0;       // first global column of this thread
-    const bool in_rows = t.row < g.lm;
-    float drow = 0.f, stile = 0.f;
-    if constexpr (MODE != BQ_GRAM) drow = a.da[size_t(t.b) * g.m + t.row];
-    if constexpr (MODE == BQ_POLY) {
-      stile = a.sa[(size_t(t.b) * mq + t.tm) * kq + t.tn];
-      // the column diagonals of this tile, shared through shared memory
-      if (t.half == 0) t.diag[t.r] = a.da[size_t(t.b) * g.m + t.col0 + t.r];
-      named_bar_sync(1, EPI_THREADS);
-    }
+  // What the tail needs from global memory besides the accumulator: the row diagonal,
+  // the tile's own block scale and this thread's 64 companion bytes (G for the polynomial,
+  // A for the update).  Fetched before the K loop so that their latency is off the tail.
+  struct Pre {
+    uint4 comp[CPT / 16];
+    float drow, stile;
+  };
+  static __device__ __forceinline__ Pre tail_prefetch(const GemmGeom& g, const Args& a, const TileCtx& t,
+                                                      int mq, int nq, int kq) {
+    Pre p;
+    p.drow = 0.f; p.stile = 0.f;
+    const int colbase = t.col0 + t.half * CPT;
+    if constexpr (MODE != BQ_GRAM) p.drow = a.da[size_t(t.b) * g.m + t.row];
+    if constexpr (MODE == BQ_POLY) p.stile = a.sa[(size_t(t.b) * mq + t.tm) * kq + t.tn];
     if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
-      stile = a.sb[(size_t(t.b) * kq + t.tm) * nq + t.tn];
-    // companion operand bytes of this thread's row: G (poly) or A (update), 128 contiguous bytes
+      p.stile = a.sb[(size_t(t.b) * kq + t.tm) * nq + t.tn];
     const uint4* comp = nullptr;
     if constexpr (MODE == BQ_POLY)
       comp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(g.a_raw) +
                                             (size_t(t.b) * g.m + t.row) * g.k + colbase);
     if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
       comp = reinterpret_cast<const uint4*>(a.row_b + (size_t(t.b) * g.m + t.row) * g.n + colbase);
+#pragma unroll
+    for (int i = 0; i < CPT / 16; ++i) p.comp[i] = comp ? comp[i] : make_uint4(0u, 0u, 0u, 0u);
+    return p;
+  }
+
+  // ---------------------------------------------------------------- tile tail
+  static __device__ __forceinline__ void tail(const GemmGeom& g, const Args& a, const TileCtx& t,
+                                              float (&vals)[CPT], const bool live, const Pre& pre,
+                                              int mq, int nq, int kq) {
+    const int c0 = t.half * CPT;           // first tile column of this thread
+    const int colbase = t.col0 + c0;       // first global column of this thread
+    const bool in_rows = t.row < g.lm;
+    const float drow = pre.drow, stile = pre.stile;
+    if constexpr (MODE == BQ_POLY) {
+      // the column diagonals of this tile, shared through shared memory
+      if (t.half == 0) t.diag[t.r] = a.da[size_t(t.b) * g.m + t.col0 + t.r];
+      named_bar_sync(1, EPI_THREADS);
+    }
 
     float mx = 1e-8f;
 #pragma unroll
     for (int c16 = 0; c16 < CPT / 16; ++c16) {
       uint32_t words[4] = {0u, 0u, 0u, 0u};
       if constexpr (MODE != BQ_GRAM) {
-#ifndef I8M_EXP_NO_COMP
-        const uint4 w = comp[c16];
-#else
-        const uint4 w = make_uint4(0x01020304u + c16, 0x05060708u, 0x090a0b0cu, 0x0d0e0f10u);
-#endif
+        const uint4 w = pre.comp[c16];
         words[0] = w.x; words[1] = w.y; words[2] = w.z; words[3] = w.w;
       }
 #pragma unroll
@@ -354,6 +369,11 @@ struct EpiBq {
       const int trows = (MODE == BQ_UPDATE) ? g.n : g.m;
       const int tld = (MODE == BQ_UPDATE) ? g.m : g.n;
       uint4* dst = reinterpret_cast<uint4*>(out + (size_t(t.b) * g.m + t.row) * g.n + colbase);
+      // With a staging tile in shared memory the transposed copy is written there byte by
+      // byte (conflict free: a warp's lanes are consecutive rows) and then leaves as
+      // coalesced 16-byte stores; without one, each byte goes to global memory directly.
+      uint8_t* tsm = t.tsm;
+      const bool staged_t = tsm != nullptr && !diag_tile;
 #pragma unroll
       for (int c16 = 0; c16 < CPT / 16; ++c16) {
         uint32_t w[4];
@@ -365,10 +385,10 @@ struct EpiBq {
             const int j = c16 * 16 + k4 * 4 + e;
             const uint32_t qv = bq_quant<FP8>(vals[j], multiplier);
             word |= qv << (8 * e);
-            if (!diag_tile) {
-#ifndef I8M_EXP_NO_TSTORE
+            if (staged_t) {
+              tsm[(c0 + j) * TSM_PITCH + t.r] = uint8_t(qv);
+            } else if (!diag_tile) {
               tdst[(size_t(t.b) * trows + (colbase + j)) * tld + t.row] = uint8_t(qv);
-#endif
             } else if (c0 + j <= t.r) {
               // a diagonal tile stores its lower half and mirrors it
               out[(size_t(t.b) * g.m + t.row) * g.n + colbase + j] = uint8_t(qv);
@@ -377,11 +397,21 @@ struct EpiBq {
           }
           w[k4] = word;
         }
-#ifndef I8M_EXP_NO_RSTORE
         if (!diag_tile) dst[c16] = make_uint4(w[0], w[1], w[2], w[3]);
-#else
-        if (w[0] == 0x12345678u && w[1] == 77u) dst[c16] = make_uint4(w[0], w[1], w[2], w[3]);
-#endif
+      }
+      if (tsm != nullptr) {
+        named_bar_sync(1, EPI_THREADS);  // uniform per tile: every epilogue warp takes this branch
+        if (!diag_tile) {
+          // 128 transposed rows of 128 bytes = 1024 chunks of 16 bytes over 256 threads
+          const int tid = t.ew * 32 + t.lane;
+#pragma unroll
+          for (int i = 0; i < (TILE * TILE / 16) / EPI_THREADS; ++i) {
+            const int chunk = tid + i * EPI_THREADS;
+            const int trow = chunk >> 3, part = chunk & 7;  // transposed row = original column
+            const uint4 v4 = *reinterpret_cast<const uint4*>(tsm + trow * TSM_PITCH + part * 16);
+            *reinterpret_cast<uint4*>(tdst + (size_t(t.b) * trows + (t.col0 + trow)) * tld + t.row0 + part * 16) = v4;
+          }
+        }
       }
     }
   }

@@ -45,6 +45,9 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * STAGE_BYTES);
   float* scale_ring = reinterpret_cast<float*>(ctrl + 1);  // [2][BQP_MAX_KB] products sA*sB per K block
+  uint8_t* tsm = reinterpret_cast<uint8_t*>(scale_ring + 2 * BQP_MAX_KB);  // transposed staging tile
+  static_assert(sizeof(Ctrl) % 16 == 0 && (2 * BQP_MAX_KB * sizeof(float)) % 16 == 0 && Epi::TSM_PITCH % 16 == 0,
+                "the staging tile is read with 16-byte loads");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -161,6 +164,7 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     t.r = t.q * 32 + lane;
     t.ctrl = ctrl;
     t.diag = ctrl->diag;
+    t.tsm = tsm;
     const int c0 = t.half * CPT;
     const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16) + uint32_t(c0);
     const int mq = g.m / Q, nq = g.n / Q, kq = g.k / Q;
@@ -180,6 +184,7 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     int buf = 0;
     uint32_t use = 0;
     const bool staged = nkb <= BQP_MAX_KB;
+    float next_scale = 0.f;
     for (int it = 0; it < my_tiles; ++it) {
       decode_tile(g, int(blockIdx.x) + it * int(gridDim.x), t.b, t.tm, t.tn);
       t.row0 = t.tm * Q; t.col0 = t.tn * Q;
@@ -188,10 +193,14 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       // scale products of this tile -> shared memory (a slow warp of tile it-1 cannot still
       // be reading this half of the ring: it passed this barrier of tile it-1 after that)
       float* sc = scale_ring + (it & 1) * BQP_MAX_KB;
+      const int ek = int(threadIdx.x) - 128;  // this thread's first K block of the scale staging
       if (staged) {
-        for (int k = int(threadIdx.x) - 128; k < nkb; k += 256) sc[k] = Epi::block_scale(g, args, t, k, mq, nq, kq);
+        // the first 256 products were fetched into a register during the previous tile
+        if (ek < nkb) sc[ek] = (it == 0) ? Epi::block_scale(g, args, t, ek, mq, nq, kq) : next_scale;
+        for (int k = ek + 256; k < nkb; k += 256) sc[k] = Epi::block_scale(g, args, t, k, mq, nq, kq);
         named_bar_sync(2, 256);
       }
+      const typename Epi::Pre pre = Epi::tail_prefetch(g, args, t, mq, nq, kq);
 #ifdef I8M_BQ_SCALAR
       float tot[CPT];
 #pragma unroll
@@ -236,8 +245,14 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 #pragma unroll
       for (int j = 0; j < CPT / 2; ++j) { tot[2 * j] = lane0(tot2[j]); tot[2 * j + 1] = lane1(tot2[j]); }
 #endif
+      if (staged && it + 1 < my_tiles && int(threadIdx.x) - 128 < nkb) {
+        // the next tile's scale product, so that its latency hides behind this tile's tail
+        TileCtx nt = t;
+        decode_tile(g, int(blockIdx.x) + (it + 1) * int(gridDim.x), nt.b, nt.tm, nt.tn);
+        next_scale = Epi::block_scale(g, args, nt, int(threadIdx.x) - 128, mq, nq, kq);
+      }
       // a warp that gave up still walks through the tail's barriers, without storing
-      Epi::tail(g, args, t, tot, ok, mq, nq, kq);
+      Epi::tail(g, args, t, tot, ok, pre, mq, nq, kq);
     }
   }
   tc_fence_before();

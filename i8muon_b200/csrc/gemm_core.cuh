@@ -54,7 +54,7 @@ struct GemmGeom {
   unsigned* status;
 };
 
-struct Ctrl {
+struct alignas(16) Ctrl {
   unsigned long long full[8];
   unsigned long long empty[8];
   unsigned long long acc_full[4];
@@ -78,6 +78,7 @@ struct TileCtx {
   Ctrl* ctrl;
   float* red;   // shared scratch for the tile-wide reduction (one float per epilogue warp)
   float* diag;  // shared scratch: TILE floats
+  uint8_t* tsm; // shared staging tile for transposed stores, or nullptr
 };
 
 __device__ __forceinline__ void decode_tile(const GemmGeom& g, int linear, int& b, int& tm,
@@ -353,7 +354,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     t.r = t.q * 32 + lane;
     t.row = row0 + t.r;
     t.ctrl = ctrl;
-    t.red = ctrl->red; t.diag = ctrl->diag;
+    t.red = ctrl->red; t.diag = ctrl->diag; t.tsm = nullptr;
     const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16);
     if constexpr (Epi::BLOCKQ) {
       Epi::template run_blockq<DEBUG>(g, args, t, taddr, abort_flag);

@@ -153,7 +153,8 @@ int launch_bq(const void* a, const void* bt, int batch, int m, int n, int k, int
   if (batch < 1 || m < 1 || n < 1 || k < 1) return fail(I8M_E_ARGUMENT, "%s: empty problem", name);
   if (!a || !bt || !status) return fail(I8M_E_ARGUMENT, "%s: null operand or status pointer", name);
   if (sym && m != n) return fail(I8M_E_ARGUMENT, "%s: symmetric product needs m == n", name);
-  constexpr size_t SMEM = size_t(BQP_STAGES) * 2 * TILE_BYTES + sizeof(Ctrl) + 2 * BQP_MAX_KB * sizeof(float) + 1024;
+  constexpr size_t SMEM = size_t(BQP_STAGES) * 2 * TILE_BYTES + sizeof(Ctrl) + 2 * BQP_MAX_KB * sizeof(float) +
+                          Epi::TSM_BYTES + 1024;
   GemmGeom g;
   g.batch = batch; g.m = m; g.n = n; g.k = k; g.lm = lm; g.ln = ln;
   g.tiles_m = cdiv(m, TILE); g.tiles_n = cdiv(n, TILE);
