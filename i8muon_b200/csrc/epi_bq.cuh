@@ -43,10 +43,14 @@ struct BqArgs {
   int out_dtype, transpose;
 };
 
+// int8 <-> float without the conversion unit (its rate is a quarter of the FP32 lanes):
+//   decode   float(q) = as_float(0x4B400000 + q) - 12582912    (exact for |q| <= 127)
+//   quantise trunc(|x|) = low bits of as_uint(|x| + 8388608 rounded toward zero), |x| < 2^23,
+//            then the sign is put back; identical to clamp(cvt.rzi(x), -127, 127).
 template <bool FP8>
 __device__ __forceinline__ float bq_decode(uint8_t v) {
   if constexpr (FP8) return e4m3_to_float(v);
-  else return float(int(int8_t(v)));
+  else return __fadd_rn(__uint_as_float(0x4B400000u + uint32_t(int(int8_t(v)))), -12582912.0f);
 }
 template <bool FP8>
 __device__ __forceinline__ uint8_t bq_quant(float v, float multiplier) {
@@ -54,7 +58,10 @@ __device__ __forceinline__ uint8_t bq_quant(float v, float multiplier) {
   if constexpr (FP8) {
     return uint8_t(__nv_cvt_float_to_fp8(fmaxf(-448.f, x), __NV_SATFINITE, __NV_E4M3));
   } else {
-    return uint8_t(int8_t(max(-127, min(127, __float2int_rz(x)))));
+    const float ax = fminf(fabsf(x), 127.f);                      // |x| <= 127 * (1 + 2^-23) in exact arithmetic
+    const uint32_t mag = __float_as_uint(__fadd_rz(ax, 8388608.0f)) & 0xffu;   // trunc(|x|)
+    const int q = (__float_as_uint(x) >> 31) ? -int(mag) : int(mag);
+    return uint8_t(int8_t(q));
   }
 }
 

@@ -128,7 +128,26 @@ struct EpiFloat {
       if (!row_ok) return;
       const int ncol = min(32, g.n - colb);
       if constexpr (MODE == MODE_FINAL) {
-        if (t.row < g.lm) {
+        // a thread's 32 consecutive outputs leave as 16-byte stores when the row is aligned
+        const size_t fbase = (size_t(t.b) * g.lm + t.row) * g.ln + colb;
+        const int esz = a.out_dtype == DT_F32 ? 4 : 2;
+        const bool wide = !a.transpose && t.row < g.lm && colb + 32 <= g.ln &&
+                          ((reinterpret_cast<uintptr_t>(a.out) + fbase * esz) & 15u) == 0;
+        if (wide) {
+          if (a.out_dtype == DT_F32) {
+            store_row<float>(static_cast<float*>(a.out) + fbase, val, 32);
+          } else if (a.out_dtype == DT_F16) {
+            alignas(16) __half hv[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) hv[j] = __float2half_rn(val[j]);
+            store_row<__half>(static_cast<__half*>(a.out) + fbase, hv, 32);
+          } else {
+            alignas(16) __nv_bfloat16 bv[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) bv[j] = __float2bfloat16_rn(val[j]);
+            store_row<__nv_bfloat16>(static_cast<__nv_bfloat16*>(a.out) + fbase, bv, 32);
+          }
+        } else if (t.row < g.lm) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int col = colb + j;

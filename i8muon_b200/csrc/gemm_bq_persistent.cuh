@@ -201,15 +201,9 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         named_bar_sync(2, 256);
       }
       const typename Epi::Pre pre = Epi::tail_prefetch(g, args, t, mq, nq, kq);
-#ifdef I8M_BQ_SCALAR
-      float tot[CPT];
-#pragma unroll
-      for (int j = 0; j < CPT; ++j) tot[j] = 0.f;
-#else
       unsigned long long tot2[CPT / 2];
 #pragma unroll
       for (int j = 0; j < CPT / 2; ++j) tot2[j] = 0ull;
-#endif
       const int gk0 = it * nkb;
 #pragma unroll 1
       for (int kb = 0; kb < nkb && ok; ++kb) {
@@ -227,11 +221,7 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           tmem_st32_fill(taddr + uint32_t(buf * Q), I8_MAGIC_BITS);
           tmem_st32_fill(taddr + uint32_t(buf * Q + 32), I8_MAGIC_BITS);
         }
-#ifdef I8M_BQ_SCALAR
-        Epi::fold64(tot, v, s);
-#else
         Epi::fold64p(tot2, v, s);
-#endif
         if (refill) tmem_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -240,11 +230,9 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       }
       if (!ok && lane == 0)
         atomicCAS(g.status, 0u, unsigned(ST_EPILOGUE_TIMEOUT) | unsigned(blockIdx.x & 0xff));
-#ifndef I8M_BQ_SCALAR
       float tot[CPT];
 #pragma unroll
       for (int j = 0; j < CPT / 2; ++j) { tot[2 * j] = lane0(tot2[j]); tot[2 * j + 1] = lane1(tot2[j]); }
-#endif
       if (staged && it + 1 < my_tiles && int(threadIdx.x) - 128 < nkb) {
         // the next tile's scale product, so that its latency hides behind this tile's tail
         TileCtx nt = t;
