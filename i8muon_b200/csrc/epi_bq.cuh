@@ -111,6 +111,16 @@ struct EpiBq {
   using Args = BqArgs;
   static constexpr float QMAX = FP8 ? 448.f : 127.f;
 
+  // The two factors of a K block's scale product, for callers that fetch them long before
+  // the multiplication (the product itself would wait for both loads where it is written).
+  static __device__ __forceinline__ void block_scale_factors(const GemmGeom& g, const Args& a, const TileCtx& t,
+                                                             int kb, int mq, int nq, int kq, float& fa, float& fb) {
+    if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
+      fb = a.sb[(size_t(t.b) * kq + kb) * nq + t.tn];
+    else
+      fb = a.sb[(size_t(t.b) * nq + t.tn) * kq + kb];
+    fa = a.sa[(size_t(t.b) * mq + t.tm) * kq + kb];
+  }
   static __device__ __forceinline__ float block_scale(const GemmGeom& g, const Args& a,
                                                       const TileCtx& t, int kb, int mq, int nq,
                                                       int kq) {

@@ -168,6 +168,7 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int c0 = t.half * CPT;
     const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16) + uint32_t(c0);
     const int mq = g.m / Q, nq = g.n / Q, kq = g.k / Q;
+    uint32_t magic[32];
     if constexpr (Epi::PRESET) {
 #pragma unroll
       for (int i = 0; i < NBUF; ++i) {
@@ -175,6 +176,12 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         tmem_st32_fill(taddr + uint32_t(i * Q + 32), I8_MAGIC_BITS);
       }
       tmem_wait_st();
+      // Every refill stores from these 32 registers.  A store of one replicated register
+      // makes the compiler copy it into 32 consecutive registers before every store (64
+      // moves per K block on the FP32 pipe); values read back from tensor memory are opaque
+      // to it and stay where the load put them.
+      tmem_ld32(taddr, magic);
+      tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0)
@@ -184,7 +191,7 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     int buf = 0;
     uint32_t use = 0;
     const bool staged = nkb <= BQP_MAX_KB;
-    float next_scale = 0.f;
+    float next_fa = 0.f, next_fb = 0.f;  // factors of the next tile's first scale products
     for (int it = 0; it < my_tiles; ++it) {
       decode_tile(g, int(blockIdx.x) + it * int(gridDim.x), t.b, t.tm, t.tn);
       t.row0 = t.tm * Q; t.col0 = t.tn * Q;
@@ -196,7 +203,7 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const int ek = int(threadIdx.x) - 128;  // this thread's first K block of the scale staging
       if (staged) {
         // the first 256 products were fetched into a register during the previous tile
-        if (ek < nkb) sc[ek] = (it == 0) ? Epi::block_scale(g, args, t, ek, mq, nq, kq) : next_scale;
+        if (ek < nkb) sc[ek] = (it == 0) ? Epi::block_scale(g, args, t, ek, mq, nq, kq) : __fmul_rn(next_fa, next_fb);
         for (int k = ek + 256; k < nkb; k += 256) sc[k] = Epi::block_scale(g, args, t, k, mq, nq, kq);
         named_bar_sync(2, 256);
       }
@@ -204,29 +211,53 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       unsigned long long tot2[CPT / 2];
 #pragma unroll
       for (int j = 0; j < CPT / 2; ++j) tot2[j] = 0ull;
-      const int gk0 = it * nkb;
-#pragma unroll 1
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        const float s = staged ? sc[kb] : Epi::block_scale(g, args, t, kb, mq, nq, kq);
-        ok = mbar_wait(accf0 + 8u * uint32_t(buf), use & 1u, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);  // keep the warp together for tcgen05.ld
-        if (!ok) break;
+      // One K block: wait for its accumulator, pull this thread's 64 columns into registers,
+      // refill the accumulator with the bias constant (INT8), fold, hand the buffer back.
+      // Written for few instructions: the loop runs 8 warps x K/128 times per tile and its
+      // bookkeeping competes with the arithmetic for issue slots.  Every K block refills,
+      // also the last ones of the launch whose buffers are not used again: no predicate.
+      const uint32_t is_lane0 = lane == 0 ? 1u : 0u;
+      auto step = [&](const uint32_t full_bar, const uint32_t empty_bar, const uint32_t tbuf,
+                      const uint32_t parity, const float s) -> bool {
+        if (!mbar_wait_warp(full_bar, parity, abort_flag)) return false;
         tc_fence_after();
         uint32_t v[2][32];
-        tmem_ld32(taddr + uint32_t(buf * Q), v[0]);
-        tmem_ld32(taddr + uint32_t(buf * Q + 32), v[1]);
+        tmem_ld32(tbuf, v[0]);
+        tmem_ld32(tbuf + 32u, v[1]);
         tmem_wait_ld();
-        const bool refill = Epi::PRESET && (gk0 + kb + NBUF < my_kb);
-        if (refill) {
-          tmem_st32_fill(taddr + uint32_t(buf * Q), I8_MAGIC_BITS);
-          tmem_st32_fill(taddr + uint32_t(buf * Q + 32), I8_MAGIC_BITS);
+        if constexpr (Epi::PRESET) {
+          tmem_st32(tbuf, magic);
+          tmem_st32(tbuf + 32u, magic);
         }
         Epi::fold64p(tot2, v, s);
-        if (refill) tmem_wait_st();
+        if constexpr (Epi::PRESET) tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(acce0 + 8u * uint32_t(buf));
-        if (++buf == NBUF) { buf = 0; ++use; }
+        mbar_arrive_if(empty_bar, is_lane0);
+        return true;
+      };
+      if (staged && (nkb & 3) == 0 && buf == 0) {
+        // every tile starts on accumulator 0: buffers and barriers are compile-time offsets,
+        // four scale products come with one shared-memory load
+        const uint32_t sc_s = smem_u32(sc);
+        uint32_t parity = use & 1u;
+#pragma unroll 1
+        for (int kb = 0; kb < nkb && ok; kb += 4) {
+          const float4 s4 = lds128(sc_s + uint32_t(kb) * 4u);
+          ok = step(accf0, acce0, taddr, parity, s4.x) &&
+               step(accf0 + 8u, acce0 + 8u, taddr + uint32_t(Q), parity, s4.y) &&
+               step(accf0 + 16u, acce0 + 16u, taddr + uint32_t(2 * Q), parity, s4.z) &&
+               step(accf0 + 24u, acce0 + 24u, taddr + uint32_t(3 * Q), parity, s4.w);
+          parity ^= 1u;
+        }
+        use += uint32_t(nkb >> 2);
+      } else {
+#pragma unroll 1
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+          const float s = staged ? sc[kb] : Epi::block_scale(g, args, t, kb, mq, nq, kq);
+          ok = step(accf0 + 8u * uint32_t(buf), acce0 + 8u * uint32_t(buf), taddr + uint32_t(buf * Q), use & 1u, s);
+          if (++buf == NBUF) { buf = 0; ++use; }
+        }
       }
       if (!ok && lane == 0)
         atomicCAS(g.status, 0u, unsigned(ST_EPILOGUE_TIMEOUT) | unsigned(blockIdx.x & 0xff));
@@ -237,7 +268,7 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         // the next tile's scale product, so that its latency hides behind this tile's tail
         TileCtx nt = t;
         decode_tile(g, int(blockIdx.x) + (it + 1) * int(gridDim.x), nt.b, nt.tm, nt.tn);
-        next_scale = Epi::block_scale(g, args, nt, int(threadIdx.x) - 128, mq, nq, kq);
+        Epi::block_scale_factors(g, args, nt, int(threadIdx.x) - 128, mq, nq, kq, next_fa, next_fb);
       }
       // a warp that gave up still walks through the tail's barriers, without storing
       Epi::tail(g, args, t, tot, ok, pre, mq, nq, kq);

@@ -67,6 +67,39 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   }
 }
 
+// The same wait for a whole warp in a hot loop: one poll and one vote on the fast path
+// (a warp-uniform branch, no divergence bookkeeping); the polling loop with its clock
+// reads lives out of line.  Returns the same value in every lane.
+__device__ __noinline__ bool mbar_wait_warp_slow(uint32_t bar, uint32_t parity,
+                                                 volatile uint32_t* abort_flag) {
+  const bool ok = mbar_wait(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
+                                               volatile uint32_t* abort_flag) {
+  const bool done = mbar_try_wait(bar, parity);
+  if (__all_sync(0xffffffffu, done)) return true;
+  return mbar_wait_warp_slow(bar, parity, abort_flag);
+}
+// Arrival by the lanes whose `pred` is non-zero, as one predicated instruction.
+__device__ __forceinline__ void mbar_arrive_if(uint32_t bar, uint32_t pred) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %1, 0;\n\t"
+      "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+      ::"r"(bar), "r"(pred)
+      : "memory");
+}
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+
 // ---------------------------------------------------------------------- TMA
 // Tiled 3-D load {k, row, batch} -> shared memory, completion on an mbarrier.
 // The innermost coordinate is always a multiple of the box width (128 bytes),
@@ -131,6 +164,19 @@ __device__ __forceinline__ void tmem_st32_fill(uint32_t taddr, uint32_t v) {
       "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
       "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
       ::"r"(taddr), "r"(v)
+      : "memory");
+}
+
+// One warp writes 32 lanes x 32 consecutive 32-bit columns from 32 registers per thread.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
 
