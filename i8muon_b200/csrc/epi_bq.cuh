@@ -58,10 +58,10 @@ __device__ __forceinline__ uint8_t bq_quant(float v, float multiplier) {
   if constexpr (FP8) {
     return uint8_t(__nv_cvt_float_to_fp8(fmaxf(-448.f, x), __NV_SATFINITE, __NV_E4M3));
   } else {
-    const float ax = fminf(fabsf(x), 127.f);                      // |x| <= 127 * (1 + 2^-23) in exact arithmetic
-    const uint32_t mag = __float_as_uint(__fadd_rz(ax, 8388608.0f)) & 0xffu;   // trunc(|x|)
-    const int q = (__float_as_uint(x) >> 31) ? -int(mag) : int(mag);
-    return uint8_t(int8_t(q));
+    // |x| <= 127 * (1 + 2^-23): the multiplier is 127 / (block maximum), so no clamp is needed
+    const uint32_t zb = __float_as_uint(__fadd_rz(fabsf(x), 8388608.0f));   // low byte = trunc(|x|)
+    const uint32_t sm = uint32_t(int(__float_as_uint(x)) >> 31);            // 0 or all ones
+    return uint8_t(((zb & 0xffu) ^ sm) - sm);                               // two's complement of the sign
   }
 }
 
@@ -282,6 +282,9 @@ struct EpiBq {
     const int c0 = t.half * CPT;           // first tile column of this thread
     const int colbase = t.col0 + c0;       // first global column of this thread
     const bool in_rows = t.row < g.lm;
+    // thread-uniform shortcuts: most threads own no padding and no diagonal element
+    const bool inside = in_rows && colbase + CPT <= g.ln;
+    const bool has_diag = (MODE == BQ_GRAM || MODE == BQ_POLY) && t.tm == t.tn;
     const float drow = pre.drow, stile = pre.stile;
     if constexpr (MODE == BQ_POLY) {
       // the column diagonals of this tile, shared through shared memory
@@ -303,7 +306,7 @@ struct EpiBq {
         const int col = colbase + j;
         float val = vals[j];
         if constexpr (MODE == BQ_GRAM) {
-          if (col == t.row) {
+          if (has_diag && col == t.row) {
             if (live) a.dout[size_t(t.b) * g.m + t.row] = in_rows ? val : 0.f;
             val = 0.f;
           }
@@ -315,7 +318,7 @@ struct EpiBq {
             val = __fadd_rn(val, __fmul_rn(__fadd_rn(drow, dcol), v));
             val = __fmul_rn(val, a.cc);
             val = __fadd_rn(val, __fmul_rn(v, a.cb));
-            if (col == t.row) {
+            if (has_diag && col == t.row) {
               const float dpoly =
                   __fadd_rn(a.ca, __fmul_rn(drow, __fadd_rn(a.cb, __fmul_rn(drow, a.cc))));
               if (live) a.dout[size_t(t.b) * g.m + t.row] = in_rows ? __fadd_rn(val, dpoly) : 0.f;
@@ -325,7 +328,7 @@ struct EpiBq {
             val = __fadd_rn(val, __fmul_rn(__fmul_rn(bq_decode<FP8>(q), drow), stile));
           }
         }
-        if (!in_rows || col >= g.ln) val = 0.f;  // padding never contributes to a block scale
+        if (!inside && (!in_rows || col >= g.ln)) val = 0.f;  // padding never contributes to a block scale
         mx = fmaxf(mx, fabsf(val));
         vals[j] = val;
       }
@@ -391,6 +394,7 @@ struct EpiBq {
       // coalesced 16-byte stores; without one, each byte goes to global memory directly.
       uint8_t* tsm = t.tsm;
       const bool staged_t = tsm != nullptr && !diag_tile;
+      const uint32_t tsm_s = tsm ? smem_u32(tsm) + uint32_t(c0 * TSM_PITCH + t.r) : 0u;
 #pragma unroll
       for (int c16 = 0; c16 < CPT / 16; ++c16) {
         uint32_t w[4];
@@ -403,7 +407,7 @@ struct EpiBq {
             const uint32_t qv = bq_quant<FP8>(vals[j], multiplier);
             word |= qv << (8 * e);
             if (staged_t) {
-              tsm[(c0 + j) * TSM_PITCH + t.r] = uint8_t(qv);
+              sts8(tsm_s + uint32_t(j * TSM_PITCH), qv);
             } else if (!diag_tile) {
               tdst[(size_t(t.b) * trows + (colbase + j)) * tld + t.row] = uint8_t(qv);
             } else if (c0 + j <= t.r) {
@@ -425,7 +429,7 @@ struct EpiBq {
           for (int i = 0; i < (TILE * TILE / 16) / EPI_THREADS; ++i) {
             const int chunk = tid + i * EPI_THREADS;
             const int trow = chunk >> 3, part = chunk & 7;  // transposed row = original column
-            const uint4 v4 = *reinterpret_cast<const uint4*>(tsm + trow * TSM_PITCH + part * 16);
+            const uint4 v4 = lds128u(smem_u32(tsm) + uint32_t(trow * TSM_PITCH + part * 16));
             *reinterpret_cast<uint4*>(tdst + (size_t(t.b) * trows + (t.col0 + trow)) * tld + t.row0 + part * 16) = v4;
           }
         }

@@ -114,6 +114,8 @@ class ShardedMuonStep:
         self.plan = build_plan(shapes, keys, self.world, steps)
         self.max_group_bytes = max_group_bytes
         self._staging: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self._copy_stream = None
+        self._consumed: Dict[int, object] = {}   # chunk -> event: its gradients were read
 
     def _buffers_for(self, g: ShardGroup, width: int, like: torch.Tensor, parity: int):
         # two staging sets per signature: chunk n+1 is produced while chunk n is gathered and applied
@@ -125,30 +127,74 @@ class ShardedMuonStep:
             hit = self._staging[key] = (send, recv)
         return hit
 
-    def step(self, params, grads, buffers) -> None:
-        pending = []
-        issued = 0
+    def _chunks(self, grads):
+        """(group, first slot, width, staging parity) in the order the step consumes them."""
+        out = []
         for g in self.plan.groups:
             like = grads[g.members[0]]
             per_matrix = like.numel() * like.element_size()
             # bound the stacked batch: process the group's slots in column chunks
             chunk = max(1, min(g.width, self.max_group_bytes // max(1, per_matrix)))
             for first in range(0, g.width, chunk):
-                width = min(chunk, g.width - first)
-                mine = g.slots[self.rank][first:first + width]
-                send, recv = self._buffers_for(g, width, like, issued & 1)
-                issued += 1
-                if mine:
-                    self.ops.momentum([grads[i] for i in mine], [buffers[i] for i in mine], send)
-                    send[:len(mine)].copy_(self.ops.orthogonalise(send[:len(mine)]))
-                if self.world > 1:
-                    work = dist.all_gather_into_tensor(recv, send, group=self.group, async_op=True)
-                else:
-                    work, recv = None, send
-                pending.append((g, first, width, recv, work))
-                # apply the previous chunk while this chunk's collective is in flight
-                if len(pending) > 1:
-                    self._apply(params, *pending.pop(0))
+                out.append((g, first, min(chunk, g.width - first), len(out) & 1))
+        return out
+
+    def _stream_gradients(self, chunks, grads, host_grads):
+        """Queue the host-to-device copies of every chunk this rank owns on a copy stream.
+
+        Returns one "ready" event per chunk.  The copy of a chunk waits for the previous step's
+        momentum kernel of the same chunk (the only reader of those gradient tensors), so the
+        copies of step n+1 run under the Newton-Schulz kernels of step n and of earlier chunks.
+        """
+        device = grads[chunks[0][0].members[0]].device
+        if device.type != "cuda":
+            for g, first, width, _ in chunks:
+                for i in g.slots[self.rank][first:first + width]:
+                    grads[i].copy_(host_grads[i])
+            return [None] * len(chunks)
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=device)
+        ready = []
+        with torch.cuda.stream(self._copy_stream):
+            for c, (g, first, width, _) in enumerate(chunks):
+                consumed = self._consumed.get(c)
+                if consumed is not None:
+                    self._copy_stream.wait_event(consumed)
+                for i in g.slots[self.rank][first:first + width]:
+                    grads[i].copy_(host_grads[i], non_blocking=True)
+                event = torch.cuda.Event()
+                event.record(self._copy_stream)
+                ready.append(event)
+        return ready
+
+    def step(self, params, grads, buffers, host_grads=None) -> None:
+        """One step.  With ``host_grads`` (pinned host tensors, indexed like ``grads``) the
+        gradients of the matrices this rank owns are first copied into ``grads`` on a separate
+        stream, chunk by chunk, overlapped with the kernels of the chunks before them."""
+        chunks = self._chunks(grads)
+        ready = self._stream_gradients(chunks, grads, host_grads) if host_grads is not None else None
+        pending = []
+        for c, (g, first, width, parity) in enumerate(chunks):
+            like = grads[g.members[0]]
+            mine = g.slots[self.rank][first:first + width]
+            send, recv = self._buffers_for(g, width, like, parity)
+            if mine:
+                if ready is not None and ready[c] is not None:
+                    torch.cuda.current_stream(like.device).wait_event(ready[c])
+                self.ops.momentum([grads[i] for i in mine], [buffers[i] for i in mine], send)
+                if ready is not None and like.device.type == "cuda":
+                    consumed = torch.cuda.Event()
+                    consumed.record(torch.cuda.current_stream(like.device))
+                    self._consumed[c] = consumed
+                send[:len(mine)].copy_(self.ops.orthogonalise(send[:len(mine)]))
+            if self.world > 1:
+                work = dist.all_gather_into_tensor(recv, send, group=self.group, async_op=True)
+            else:
+                work, recv = None, send
+            pending.append((g, first, width, recv, work))
+            # apply the previous chunk while this chunk's collective is in flight
+            if len(pending) > 1:
+                self._apply(params, *pending.pop(0))
         while pending:
             self._apply(params, *pending.pop(0))
 

@@ -190,3 +190,36 @@ def test_example_training_loop(cuda_device):
             losses.append(loss.item())
         check_status()
         assert all(np.isfinite(losses)) and losses[-1] < losses[0]
+
+
+def test_sharded_step_streams_host_gradients(cuda_device):
+    """`ShardedMuonStep.step(host_grads=...)`: pinned host gradients copied chunk by chunk on a side
+    stream give bit-identical parameters and momentum to the same steps on resident gradients,
+    over several steps (the copies of step n+1 may only start once step n has read a chunk)."""
+    from i8muon_b200.optimizer import native_step_ops
+    from i8muon_b200.sharding import ShardedMuonStep
+    g = torch.Generator().manual_seed(33)
+    shapes = [(256, 384)] * 5 + [(384, 256)] * 2 + [(128, 128)] * 3
+    host = [[(torch.randn(s, generator=g) * 1e-3).bfloat16().pin_memory() for s in shapes] for _ in range(3)]
+    start = [(torch.randn(s, generator=g) * 0.02).bfloat16() for s in shapes]
+    engine = CutlassNSInt8()
+    ops = native_step_ops(engine, lr=0.02, weight_decay=0.01, momentum=0.95, ns_coefficients=C5,
+                          adjust_lr_fn="match_rms_adamw", precision="int8_bq", use_gram=False)
+    results = []
+    for streamed in (False, True):
+        params = [p.clone().to(cuda_device) for p in start]
+        landing = [torch.zeros(s, dtype=torch.bfloat16, device=cuda_device) for s in shapes]
+        stepper = ShardedMuonStep(params, 5, ops, max_group_bytes=2 * 256 * 384 * 2)  # several chunks per group
+        buffers = {i: torch.zeros_like(landing[i]) for i in stepper.plan.owned(0)}
+        for step_grads in host:
+            if streamed:
+                stepper.step(params, landing, buffers, host_grads=step_grads)
+            else:
+                stepper.step(params, [t.to(cuda_device) for t in step_grads], buffers)
+        torch.cuda.synchronize()
+        check_status()
+        results.append((params, buffers))
+    for a, b in zip(results[0][0], results[1][0]):
+        assert torch.equal(a, b)
+    for i in results[0][1]:
+        assert torch.equal(results[0][1][i], results[1][1][i])

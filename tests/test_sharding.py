@@ -113,3 +113,20 @@ def test_sharded_step_equals_unsharded(world):
                 assert torch.equal(b, want_bufs[i])  # momentum lives with its owner
             seen |= set(got["owned"])
         assert seen == set(range(len(want_params)))
+
+
+def test_step_with_host_gradients_equals_step_with_resident_gradients():
+    """`host_grads` copies each owned gradient into the device-side tensor before its chunk runs
+    (on CPU tensors the copy is synchronous; the stream/event plumbing is covered by the GPU test)."""
+    want_params, want_bufs = expected()
+    params, bufs, grads = make_problem()
+    ops = cpu_ops((0.95, 0.9), 0.02, 0.01, "base_lr", "spectral")
+    stepper = ShardedMuonStep(params, steps=5, ops=ops, max_group_bytes=2 * 24 * 40 * 2)
+    buffers = {i: bufs[i] for i in stepper.plan.owned(0)}
+    landing = [torch.zeros_like(g) for g in grads[0]]
+    for step_grads in grads:
+        stepper.step(params, landing, buffers, host_grads=step_grads)
+    for p, w in zip(params, want_params):
+        assert torch.equal(p, w)
+    for i, b in buffers.items():
+        assert torch.equal(b, want_bufs[i])
