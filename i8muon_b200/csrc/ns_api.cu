@@ -321,7 +321,22 @@ extern "C" int i8m_normalize(const void* x, int in_dtype, const float* norm, voi
                                 static_cast<const In*>(x), norm, static_cast<E*>(a),           \
                                 static_cast<E*>(a_t), static_cast<float*>(a_lo),               \
                                 static_cast<float*>(a_t_lo), rows, cols, lp, hp, transpose, eps)))
-  if (compute == I8M_F32) NORM_LAUNCH(float);
+  // 16-bit in and out, rows of whole 16-byte vectors: the vectorised kernel
+  const bool vec = in_dtype != I8M_F32 && compute != I8M_F32 && cols % 8 == 0 && lp % 8 == 0 && hp % 8 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a) |
+                     reinterpret_cast<uintptr_t>(a_t)) & 15u) == 0;
+  if (vec) {
+    dim3 vgrid(cdiv(pcol, 64), cdiv(prow, 64), batch);
+#define NORM_VEC(In, E)                                                                              \
+  normalize_vec_kernel<In, E><<<vgrid, 256, 0, S(stream)>>>(static_cast<const In*>(x), norm,         \
+                                                            static_cast<E*>(a), static_cast<E*>(a_t), \
+                                                            rows, cols, lp, hp, transpose, eps)
+    if (in_dtype == I8M_F16 && compute == I8M_F16) NORM_VEC(__half, __half);
+    else if (in_dtype == I8M_F16) NORM_VEC(__half, __nv_bfloat16);
+    else if (compute == I8M_F16) NORM_VEC(__nv_bfloat16, __half);
+    else NORM_VEC(__nv_bfloat16, __nv_bfloat16);
+#undef NORM_VEC
+  } else if (compute == I8M_F32) NORM_LAUNCH(float);
   else if (compute == I8M_F16) NORM_LAUNCH(__half);
   else NORM_LAUNCH(__nv_bfloat16);
 #undef NORM_LAUNCH
@@ -439,7 +454,19 @@ extern "C" int i8m_bq_quant(const void* x, int in_dtype, const float* norm, void
   dim3 grid(lp / 128, hp / 128, batch);
   if (grid.y > 65535) return fail(I8M_E_LIMIT, "bq_quant: matrix too wide");
   const float e = norm ? eps : 0.f;
-  if (fp8)
+  const bool vec = in_dtype != I8M_F32 && cols % 8 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a) |
+                     reinterpret_cast<uintptr_t>(a_t)) & 15u) == 0;
+  if (vec) {
+#define BQ_VEC(In, F8)                                                                                  \
+  bq_quant_vec_kernel<In, F8><<<grid, 256, 0, S(stream)>>>(static_cast<const In*>(x), norm,             \
+                                                           static_cast<uint8_t*>(a),                    \
+                                                           static_cast<uint8_t*>(a_t), scale, rows, cols, \
+                                                           lp, hp, transpose, e)
+    if (in_dtype == I8M_F16) { if (fp8) BQ_VEC(__half, true); else BQ_VEC(__half, false); }
+    else { if (fp8) BQ_VEC(__nv_bfloat16, true); else BQ_VEC(__nv_bfloat16, false); }
+#undef BQ_VEC
+  } else if (fp8)
     DISPATCH_IN(in_dtype, In, (bq_quant_kernel<In, true><<<grid, 256, 0, S(stream)>>>(
                                   static_cast<const In*>(x), norm, static_cast<uint8_t*>(a),
                                   static_cast<uint8_t*>(a_t), scale, rows, cols, lp, hp, transpose, e)));

@@ -144,6 +144,139 @@ normalize_kernel(const In* x, const float* norm, E* out, E* out_t, float* out_lo
   }
 }
 
+// Vectorised flavours of the two prologues for 16-bit inputs whose rows are a multiple of
+// eight elements and 16-byte aligned: every global access is a 16-byte (8-byte for the INT8
+// row-major output) coalesced vector, and the transposed copy goes through a shared tile that
+// is already stored transposed.  The tile rows are 128 bytes; their 16-byte units are XOR-ed
+// with (column / 8) % 8, which spreads the column-wise element stores of a warp over all banks
+// and keeps the row-wise 16-byte loads of the copy-out conflict free.  Same arithmetic, same
+// results as the scalar kernels above.
+__device__ __forceinline__ uint32_t swz16(int c) { return uint32_t((c >> 3) & 7) << 4; }
+
+template <typename In>
+__device__ __forceinline__ void unpack8(const uint4 raw, float (&v)[8]) {
+  const In* e = reinterpret_cast<const In*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = widen<In>(e[j]);
+}
+
+// 64 x 64 tile of the input per block of 256 threads; In and E are 16-bit types.
+template <typename In, typename E>
+__global__ void __launch_bounds__(256)
+normalize_vec_kernel(const In* x, const float* norm, E* out, E* out_t, int rows, int cols, int m, int n,
+                     int transpose, float eps) {
+  __shared__ __align__(16) uint8_t tile_t[64 * 128];   // [input column][input row] of E, swizzled
+  const int b = blockIdx.z;
+  const float nb = norm ? norm[b] : 1.f;
+  const float inv = nb == 0.f ? 0.f : 1.f / fmaxf(nb, eps);
+  const int prow = transpose ? n : m, pcol = transpose ? m : n;
+  E* primary = transpose ? out_t : out;
+  E* secondary = transpose ? out : out_t;
+  const int row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int id = int(threadIdx.x) + 256 * i;
+    const int r = id >> 3, part = id & 7;
+    const int row = row0 + r, col = col0 + part * 8;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    if (row < rows && col < cols) {
+      unpack8<In>(*reinterpret_cast<const uint4*>(x + (size_t(b) * rows + row) * cols + col), v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(v[j], inv);
+    }
+    alignas(16) E e[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = round_to<E>(v[j]);
+    if (primary != nullptr && row < prow && col < pcol)
+      *reinterpret_cast<uint4*>(primary + (size_t(b) * prow + row) * pcol + col) = *reinterpret_cast<const uint4*>(e);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = part * 8 + j;
+      *reinterpret_cast<E*>(tile_t + c * 128 + ((uint32_t(r) * 2u) ^ swz16(c))) = e[j];
+    }
+  }
+  __syncthreads();
+  if (secondary == nullptr) return;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int id = int(threadIdx.x) + 256 * i;
+    const int c = id >> 3, p = id & 7;   // transposed row = input column, 16-byte unit = 8 input rows
+    const int trow = col0 + c, tcol = row0 + p * 8;
+    if (trow < pcol && tcol < prow)
+      *reinterpret_cast<uint4*>(secondary + (size_t(b) * pcol + trow) * prow + tcol) =
+          *reinterpret_cast<const uint4*>(tile_t + c * 128 + ((uint32_t(p) * 16u) ^ swz16(c)));
+  }
+}
+
+// One 128 x 128 quantisation block per block of 256 threads; In is a 16-bit type.
+template <typename In, bool FP8>
+__global__ void __launch_bounds__(256)
+bq_quant_vec_kernel(const In* x, const float* norm, uint8_t* out, uint8_t* out_t, float* scale,
+                    int rows, int cols, int m, int n, int transpose, float eps) {
+  __shared__ float sh[8];
+  __shared__ float s_mult;
+  __shared__ __align__(16) uint8_t tile_t[128 * 128];   // [input column][input row] bytes, swizzled
+  const int tmb = blockIdx.x, tnb = blockIdx.y, b = blockIdx.z;
+  const float nb = norm ? norm[b] : 1.f;
+  float inv = 1.f / fmaxf(nb, eps);
+  if (nb == 0.f) inv = 0.f;
+  // the patch in the INPUT's orientation: without transpose its rows are the block's rows
+  const int ir0 = transpose ? tnb * 128 : tmb * 128, ic0 = transpose ? tmb * 128 : tnb * 128;
+  float vals[8][8];
+  float mx = 1e-8f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int id = int(threadIdx.x) + 256 * i;
+    const int r = id >> 4, part = id & 15;
+    const int ir = ir0 + r, ic = ic0 + part * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) vals[i][j] = 0.f;
+    if (ir < rows && ic < cols) {
+      unpack8<In>(*reinterpret_cast<const uint4*>(x + (size_t(b) * rows + ir) * cols + ic), vals[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vals[i][j] = __fmul_rn(vals[i][j], inv);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(vals[i][j]));
+  }
+  mx = block_max_256(mx, sh);
+  if (threadIdx.x == 0) {
+    const float multiplier = (FP8 ? 448.f : 127.f) / mx;
+    s_mult = multiplier;
+    scale[(size_t(b) * (m / 128) + tmb) * (n / 128) + tnb] = 1.f / multiplier;
+  }
+  __syncthreads();
+  const float multiplier = s_mult;
+  uint8_t* same = transpose ? out_t : out;     // shares the input's orientation
+  uint8_t* other = transpose ? out : out_t;
+  const int sld = transpose ? m : n, srows = transpose ? n : m;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int id = int(threadIdx.x) + 256 * i;
+    const int r = id >> 4, part = id & 15;
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t q = bq_quant<FP8>(vals[i][j], multiplier);
+      w[j >> 2] |= q << (8 * (j & 3));
+      const int c = part * 8 + j;
+      tile_t[c * 128 + (uint32_t(r) ^ swz16(c))] = uint8_t(q);
+    }
+    *reinterpret_cast<uint2*>(same + (size_t(b) * srows + ir0 + r) * sld + ic0 + part * 8) = make_uint2(w[0], w[1]);
+  }
+  __syncthreads();
+  const int old = transpose ? n : m, orows = transpose ? m : n;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int id = int(threadIdx.x) + 256 * i;
+    const int c = id >> 3, p = id & 7;   // transposed row = input column, 16 input rows per unit
+    *reinterpret_cast<uint4*>(other + (size_t(b) * orows + ic0 + c) * old + ir0 + p * 16) =
+        *reinterpret_cast<const uint4*>(tile_t + c * 128 + ((uint32_t(p) * 16u) ^ swz16(c)));
+  }
+}
+
 // ------------------------------------------------------------ input quant
 // Global-scale INT8 quantisation of the input (round half to even), its
 // transpose, and a_scale[b] = amax / (127 * max(norm, eps)); restates
