@@ -208,6 +208,13 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         named_bar_sync(2, 256);
       }
       const typename Epi::Pre pre = Epi::tail_prefetch(g, args, t, mq, nq, kq);
+      if (staged && it + 1 < my_tiles && int(threadIdx.x) - 128 < nkb) {
+        // the factors of the next tile's scale products: fetched here so that the address
+        // arithmetic and the loads' latency lie under this tile's K loop, not in its tail
+        TileCtx nt = t;
+        decode_tile(g, int(blockIdx.x) + (it + 1) * int(gridDim.x), nt.b, nt.tm, nt.tn);
+        Epi::block_scale_factors(g, args, nt, int(threadIdx.x) - 128, mq, nq, kq, next_fa, next_fb);
+      }
       unsigned long long tot2[CPT / 2];
 #pragma unroll
       for (int j = 0; j < CPT / 2; ++j) tot2[j] = 0ull;
@@ -264,12 +271,6 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       float tot[CPT];
 #pragma unroll
       for (int j = 0; j < CPT / 2; ++j) { tot[2 * j] = lane0(tot2[j]); tot[2 * j + 1] = lane1(tot2[j]); }
-      if (staged && it + 1 < my_tiles && int(threadIdx.x) - 128 < nkb) {
-        // the next tile's scale product, so that its latency hides behind this tile's tail
-        TileCtx nt = t;
-        decode_tile(g, int(blockIdx.x) + (it + 1) * int(gridDim.x), nt.b, nt.tm, nt.tn);
-        Epi::block_scale_factors(g, args, nt, int(threadIdx.x) - 128, mq, nq, kq, next_fa, next_fb);
-      }
       // a warp that gave up still walks through the tail's barriers, without storing
       Epi::tail(g, args, t, tot, ok, pre, mq, nq, kq);
     }
