@@ -23,17 +23,18 @@
 
 namespace i8m {
 
-constexpr int BQP_STAGES = 6;
+constexpr int BQP_STAGES = 6;        // default ring depth; the tuner may pick BQP_STAGES_ALT
+constexpr int BQP_STAGES_ALT = 4;
 constexpr int BQP_THREADS = 384;
 constexpr int BQP_MAX_KB = 512;  // K blocks whose scales are staged in shared memory (K <= 65536)
 constexpr int BQP_CTRL_REGS = 56;
 constexpr int BQP_EPI_REGS = 224;
 
-template <class Epi>
+template <class Epi, int STAGES_T>
 __global__ void __launch_bounds__(BQP_THREADS, 1)
 bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      GemmGeom g, typename Epi::Args args) {
-  constexpr int STAGES = BQP_STAGES;
+  constexpr int STAGES = STAGES_T;
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   constexpr int NBUF = 4;
   constexpr int Q = TILE;

@@ -23,6 +23,7 @@ namespace {
 
 thread_local char g_error[512] = "";
 int g_debug_simt = 0;
+int g_bq_variant = 0;   // 0: six-stage ring, 1: four-stage ring (chosen by the host-side tuner)
 std::atomic<unsigned long long> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
@@ -153,8 +154,9 @@ int launch_bq(const void* a, const void* bt, int batch, int m, int n, int k, int
   if (batch < 1 || m < 1 || n < 1 || k < 1) return fail(I8M_E_ARGUMENT, "%s: empty problem", name);
   if (!a || !bt || !status) return fail(I8M_E_ARGUMENT, "%s: null operand or status pointer", name);
   if (sym && m != n) return fail(I8M_E_ARGUMENT, "%s: symmetric product needs m == n", name);
-  constexpr size_t SMEM = size_t(BQP_STAGES) * 2 * TILE_BYTES + sizeof(Ctrl) + 2 * BQP_MAX_KB * sizeof(float) +
-                          Epi::TSM_BYTES + 1024;
+  const int stages = g_bq_variant == 1 ? BQP_STAGES_ALT : BQP_STAGES;
+  const size_t SMEM = size_t(stages) * 2 * TILE_BYTES + sizeof(Ctrl) + 2 * BQP_MAX_KB * sizeof(float) +
+                      Epi::TSM_BYTES + 1024;
   GemmGeom g;
   g.batch = batch; g.m = m; g.n = n; g.k = k; g.lm = lm; g.ln = ln;
   g.tiles_m = cdiv(m, TILE); g.tiles_n = cdiv(n, TILE);
@@ -169,7 +171,7 @@ int launch_bq(const void* a, const void* bt, int batch, int m, int n, int k, int
   CUtensorMap ma, mb;
   if (int rc = make_operand_map(&ma, a, 1, k, m, batch)) return rc;
   if (int rc = make_operand_map(&mb, bt, 1, k, n, batch)) return rc;
-  auto kernel = bq_persistent_kernel<Epi>;
+  auto kernel = g_bq_variant == 1 ? bq_persistent_kernel<Epi, BQP_STAGES_ALT> : bq_persistent_kernel<Epi, BQP_STAGES>;
   CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
   const unsigned grid = unsigned(std::min<long long>(tiles, sm_count()));
   kernel<<<grid, BQP_THREADS, SMEM, stream>>>(ma, mb, g, args);
@@ -230,6 +232,17 @@ extern "C" const char* i8m_last_error(void) { return g_error; }
 extern "C" unsigned long long i8m_launch_count(void) { return g_launches.load(); }
 extern "C" int i8m_set_debug_core(int simt) {
   g_debug_simt = simt ? 1 : 0;
+  return 0;
+}
+extern "C" int i8m_variant_count(const char* operation) {
+  if (operation && std::strcmp(operation, "bq_gemm") == 0) return 2;
+  return 0;
+}
+extern "C" int i8m_set_variant(const char* operation, int variant) {
+  if (!operation || std::strcmp(operation, "bq_gemm") != 0)
+    return fail(I8M_E_ARGUMENT, "set_variant: unknown operation");
+  if (variant < 0 || variant >= 2) return fail(I8M_E_ARGUMENT, "set_variant: bq_gemm has variants 0 and 1");
+  g_bq_variant = variant;
   return 0;
 }
 

@@ -13,7 +13,8 @@ Differences that a caller can observe:
   * ``deterministic`` is accepted and ignored - the norm reduction is always the
     deterministic two-pass one;
   * the result is a fresh tensor, not a view into the call's workspace;
-  * ``tiles`` is validated and recorded but the kernels use one 128x128 CTA tile.
+  * ``tiles`` is validated and recorded but the kernels use one 128x128 CTA tile; ``autotune``
+    times the library's kernel variants of the block-quantised GEMMs instead (``tuning.py``).
 """
 from __future__ import annotations
 
@@ -26,6 +27,7 @@ import torch
 from . import native
 from .coefficients import DEFAULT_COEFFICIENTS
 from .routing import matrix_spec, normalize_precision, select_route
+from .tuning import KernelFactory
 
 _COMPUTE_CODES = {"float32": native.F32, "float16": native.F16, "bfloat16": native.BF16}
 _STATUS_WORDS = {}
@@ -73,6 +75,7 @@ class CutlassNSInt8:
                 or any(v not in (0, 1, 2, 3, 4) for v in self.tiles.values())):
             raise ValueError("tiles accepts aat/square/update with values 0/1/2/3/4")
         self._routes = {}
+        self._factory = KernelFactory(autotune)
 
     # ------------------------------------------------------------ routing
     def router(self, M: int, N: int, precision: str, use_gram: bool, gram_aspect_threshold: float):
@@ -96,12 +99,21 @@ class CutlassNSInt8:
             raise ValueError("I8MUON_GRAM_RESET must be a binary string starting with 0")
         with torch.cuda.device(x.device):
             size = native.ns_workspace_bytes(route, batch, rows, cols, dtype, compute, steps, fp16_first)
-            workspace = torch.empty(size, dtype=torch.uint8, device=x.device)
             out = torch.empty_like(x)
-            native.call("i8m_ns_run", route, x.data_ptr(), out.data_ptr(), dtype, batch, rows, cols,
-                        compute, array, steps, float(eps), int(bool(fp16_first)),
-                        order.encode() if order is not None else None, workspace.data_ptr(), size,
-                        status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+
+            def launch(variant):
+                native.call("i8m_set_variant", b"bq_gemm", int(variant))
+                workspace = torch.empty(size, dtype=torch.uint8, device=x.device)
+                native.call("i8m_ns_run", route, x.data_ptr(), out.data_ptr(), dtype, batch, rows, cols,
+                            compute, array, steps, float(eps), int(bool(fp16_first)),
+                            order.encode() if order is not None else None, workspace.data_ptr(), size,
+                            status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+
+            variant = 0
+            if route in (native.ROUTE_BQ_INT8, native.ROUTE_BQ_FP8):
+                key = (x.device.index, x.dtype, batch, rows, cols, route, steps, bool(fp16_first))
+                variant = self._factory.select("bq_gemm", key, (0, 1), 0, launch)
+            launch(variant)
         # The workspace may be reused by later allocations on this stream only.
         return out.view(shape)
 

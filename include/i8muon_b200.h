@@ -60,6 +60,12 @@ unsigned long long i8m_launch_count(void);
 /* tests only: 1 replaces the TMA/tcgen05 mainloop by plain dot products inside
  * the epilogue threads (same epilogues); 0 restores the tensor-core path. */
 int i8m_set_debug_core(int simt);
+/* Kernel variants a host-side tuner can choose between, the counterpart of the tile ids
+ * that the reference's KernelFactory times (src/i8muon/_cuda_factory.py:62-102).
+ * operation "bq_gemm": 0 = six-stage operand ring (default), 1 = four-stage ring.
+ * The choice is process-wide and applies to launches made after the call. */
+int i8m_variant_count(const char* operation);
+int i8m_set_variant(const char* operation, int variant);
 
 /* ---- stage level: statistics ---------------------------------------------
  * norm[b] = ||x_b||_F (FP32 accumulate, deterministic two-pass) and

@@ -16,7 +16,7 @@ import pytest
 import torch
 
 import gpu_helpers as H
-from i8muon_b200 import CutlassNSInt8, check_status, recommend_coefficients
+from i8muon_b200 import CutlassNSInt8, check_status, native, recommend_coefficients
 from oracle import ns_oracle as o
 
 pytestmark = pytest.mark.gpu
@@ -227,3 +227,35 @@ def test_baseline_config_shapes_reduced_batch(cuda_device):
         truth = o.ns_fp32_torch(x, C5)
         assert rel(y.float(), truth) < 0.12
     check_status()
+
+
+def test_autotuned_engine_and_kernel_variants_give_identical_results(cuda_device):
+    """The tuner only chooses between schedules of the same arithmetic: the four-stage variant of
+    the block-quantised GEMM, and an engine with autotune on, reproduce the default bit for bit."""
+    g = torch.Generator().manual_seed(99)
+    x = (torch.randn((3, 256, 640), generator=g) * 0.02).bfloat16().to(cuda_device)
+    plain = CutlassNSInt8()
+    want = plain._regular_bq(x, C5, precision="int8_bq")
+    assert native.library().i8m_variant_count(b"bq_gemm") == 2
+    try:
+        native.call("i8m_set_variant", b"bq_gemm", 1)
+        # the engine sets the variant itself on every call, so drive the stage directly
+        a, at, sa = H.bq_quant(x, None, False)
+        native.call("i8m_set_variant", b"bq_gemm", 0)
+        g0 = H.bq_gemm(False, 0, a, sa, a, sa, lm=256, ln=256)
+        native.call("i8m_set_variant", b"bq_gemm", 1)
+        g1 = H.bq_gemm(False, 0, a, sa, a, sa, lm=256, ln=256)
+    finally:
+        native.call("i8m_set_variant", b"bq_gemm", 0)
+    for p, q in zip(g0, g1):
+        if isinstance(p, torch.Tensor):
+            assert torch.equal(p, q)   # quantised Gram tile, its scales and the FP32 diagonal
+    tuned = CutlassNSInt8(autotune=True)
+    got = tuned._regular_bq(x, C5, precision="int8_bq")
+    check_status()
+    assert torch.equal(got, want)
+    assert len(tuned._factory.timings) == 1
+    (scores,) = tuned._factory.timings.values()
+    assert set(scores) == {0, 1} and all(v > 0 for v in scores.values())
+    with pytest.raises(native.NativeError):
+        native.call("i8m_set_variant", b"no_such_op", 0)
