@@ -392,9 +392,12 @@ struct EpiBq {
       // With a staging tile in shared memory the transposed copy is written there byte by
       // byte (conflict free: a warp's lanes are consecutive rows) and then leaves as
       // coalesced 16-byte stores; without one, each byte goes to global memory directly.
+      // A diagonal tile (gram / poly) is its own mirror: its lower half goes to the staging
+      // tile at both positions and the whole tile leaves through the same copy-out.
       uint8_t* tsm = t.tsm;
-      const bool staged_t = tsm != nullptr && !diag_tile;
-      const uint32_t tsm_s = tsm ? smem_u32(tsm) + uint32_t(c0 * TSM_PITCH + t.r) : 0u;
+      const bool staged_t = tsm != nullptr;
+      const uint32_t tsm_s = tsm ? smem_u32(tsm) + uint32_t(c0 * TSM_PITCH + t.r) : 0u;      // (column, row)
+      const uint32_t tsm_own = tsm ? smem_u32(tsm) + uint32_t(t.r * TSM_PITCH + c0) : 0u;    // (row, column)
 #pragma unroll
       for (int c16 = 0; c16 < CPT / 16; ++c16) {
         uint32_t w[4];
@@ -407,7 +410,12 @@ struct EpiBq {
             const uint32_t qv = bq_quant<FP8>(vals[j], multiplier);
             word |= qv << (8 * e);
             if (staged_t) {
-              sts8(tsm_s + uint32_t(j * TSM_PITCH), qv);
+              if (!diag_tile) {
+                sts8(tsm_s + uint32_t(j * TSM_PITCH), qv);
+              } else if (c0 + j <= t.r) {
+                sts8(tsm_s + uint32_t(j * TSM_PITCH), qv);
+                sts8(tsm_own + uint32_t(j), qv);
+              }
             } else if (!diag_tile) {
               tdst[(size_t(t.b) * trows + (colbase + j)) * tld + t.row] = uint8_t(qv);
             } else if (c0 + j <= t.r) {
@@ -422,16 +430,15 @@ struct EpiBq {
       }
       if (tsm != nullptr) {
         named_bar_sync(1, EPI_THREADS);  // uniform per tile: every epilogue warp takes this branch
-        if (!diag_tile) {
-          // 128 transposed rows of 128 bytes = 1024 chunks of 16 bytes over 256 threads
-          const int tid = t.ew * 32 + t.lane;
+        // 128 staged rows of 128 bytes = 1024 chunks of 16 bytes over 256 threads; a staged row
+        // is a column of this tile, i.e. a row of the transposed / mirrored tile
+        const int tid = t.ew * 32 + t.lane;
 #pragma unroll
-          for (int i = 0; i < (TILE * TILE / 16) / EPI_THREADS; ++i) {
-            const int chunk = tid + i * EPI_THREADS;
-            const int trow = chunk >> 3, part = chunk & 7;  // transposed row = original column
-            const uint4 v4 = lds128u(smem_u32(tsm) + uint32_t(trow * TSM_PITCH + part * 16));
-            *reinterpret_cast<uint4*>(tdst + (size_t(t.b) * trows + (t.col0 + trow)) * tld + t.row0 + part * 16) = v4;
-          }
+        for (int i = 0; i < (TILE * TILE / 16) / EPI_THREADS; ++i) {
+          const int chunk = tid + i * EPI_THREADS;
+          const int trow = chunk >> 3, part = chunk & 7;
+          const uint4 v4 = lds128u(smem_u32(tsm) + uint32_t(trow * TSM_PITCH + part * 16));
+          *reinterpret_cast<uint4*>(tdst + (size_t(t.b) * trows + (t.col0 + trow)) * tld + t.row0 + part * 16) = v4;
         }
       }
     }
