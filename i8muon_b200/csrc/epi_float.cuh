@@ -162,7 +162,10 @@ struct EpiFloat {
         E* out = static_cast<E*>(a.out);
         float* out_lo = static_cast<float*>(a.out_lo);
         const size_t rbase = (size_t(t.b) * g.m + t.row) * g.n + colb;
-        if (!diag_tile) {
+        // 16-bit products of a symmetric pair are bitwise symmetric (same products, same
+        // accumulation order for (r, c) and (c, r); checked on the device), so a diagonal tile
+        // is stored like any other and needs no mirror.  FP32 keeps the explicit mirror.
+        if (!diag_tile || !IS_F32) {
           if constexpr (IS_F32) {
             float hi[32], lo[32];
 #pragma unroll
@@ -186,7 +189,7 @@ struct EpiFloat {
           const int col = colb + j;
           if (col >= g.n) continue;
           if (diag_tile) {
-            if (col > t.row) continue;
+            if (!IS_F32 || col > t.row) continue;
             size_t d0 = (size_t(t.b) * g.m + t.row) * g.n + col;
             size_t d1 = (size_t(t.b) * g.m + col) * g.n + t.row;
             if constexpr (IS_F32) {
