@@ -52,10 +52,12 @@ def test_stats(cuda_device, dtype):
     assert norm.abs().max() == 0 and amax.abs().max() == 0
 
 
-@pytest.mark.parametrize("shape", [(2, 48, 112), (2, 112, 48), (1, 37, 75), (1, 75, 37)])
+@pytest.mark.parametrize("shape", [(2, 48, 112), (2, 112, 48), (1, 37, 75), (1, 75, 37), (2, 200, 328), (1, 328, 200)])
 @pytest.mark.parametrize("compute", [torch.float16, torch.bfloat16, torch.float32])
 def test_normalize(cuda_device, shape, compute):
-    x = make_input(shape, torch.bfloat16, 2).to(cuda_device)
+    # widths that are multiples of eight take the vectorised kernel (16-bit compute types),
+    # the others and FP32 compute the scalar one
+    x = make_input(shape, torch.float16 if shape[1] == 200 else torch.bfloat16, 2).to(cuda_device)
     norm, _ = H.stats(x)
     a, at, alo, atlo = H.normalize(x, norm, compute)
     inv = o._inv_norm(npy(norm), 1e-7)
@@ -142,9 +144,13 @@ def test_int8_iteration_stagewise_bit_exact(cuda_device, core, l, h):
 
 # ------------------------------------------------------------------ block-quantised iteration
 @pytest.mark.parametrize("fp8", [False, True], ids=["int8", "e4m3"])
-@pytest.mark.parametrize("shape", [(2, 144, 400), (1, 400, 144), (1, 256, 512)])
-def test_bq_quant_bit_exact(cuda_device, fp8, shape):
-    x = make_input(shape, torch.bfloat16, 5, outliers=True).to(cuda_device)
+@pytest.mark.parametrize("shape,dtype", [((2, 144, 400), torch.bfloat16), ((1, 400, 144), torch.bfloat16),
+                                         ((1, 256, 512), torch.float16), ((1, 130, 203), torch.bfloat16),
+                                         ((1, 203, 130), torch.float16), ((1, 144, 400), torch.float32)])
+def test_bq_quant_bit_exact(cuda_device, fp8, shape, dtype):
+    """Rows of whole 16-byte vectors of a 16-bit type take the vectorised kernel, odd widths and
+    FP32 inputs the scalar one; both must reproduce the oracle's codes, transposes and scales."""
+    x = make_input(shape, dtype, 5, outliers=True).to(cuda_device)
     norm, _ = H.stats(x)
     a, at, sa = H.bq_quant(x, norm, fp8)
     inv = o._inv_norm(npy(norm), 1e-7)
