@@ -150,102 +150,27 @@ struct EpiBq {
       }
     }
   }
-  static __device__ __forceinline__ void fold64(float (&tot)[64], const uint32_t (&v)[2][32], const float s) {
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        float p = __uint_as_float(v[c][j]);
-        if constexpr (PRESET) p = __fadd_rn(p, -I8_MAGIC);
-        tot[c * 32 + j] = __fmaf_rn(p, s, tot[c * 32 + j]);
-      }
-    }
-  }
-
-  template <bool DEBUG>
-  static __device__ __forceinline__ void run_blockq(const GemmGeom& g, const Args& a,
-                                                    const TileCtx& t, uint32_t taddr,
-                                                    volatile uint32_t* abort_flag) {
+  // Debug core of the one-tile-per-CTA skeleton: plain dot products per K block, the same
+  // promotion arithmetic and the same tail.
+  static __device__ __forceinline__ void run_debug(const GemmGeom& g, const Args& a, const TileCtx& t) {
     constexpr int Q = TILE;
     const int mq = g.m / Q, nq = g.n / Q, kq = g.k / Q;
     const int c0 = t.half * CPT;  // first tile column of this thread
-    unsigned long long tot[CPT / 2];
-#pragma unroll
-    for (int j = 0; j < CPT / 2; ++j) tot[j] = 0ull;
-    bool ok = true;
-    if constexpr (DEBUG) {
-      // debug core: plain dot products per K block, same promotion arithmetic
-#pragma unroll 1
-      for (int kb = 0; kb < g.num_kb; ++kb) {
-        const float s = block_scale(g, a, t, kb, mq, nq, kq);
-#pragma unroll 4
-        for (int j = 0; j < CPT / 2; ++j) {
-          uint32_t v0 = simt_dot<KIND, uint8_t>(g, t.b, t.row, t.col0 + c0 + 2 * j, kb * Q, kb * Q + Q);
-          uint32_t v1 = simt_dot<KIND, uint8_t>(g, t.b, t.row, t.col0 + c0 + 2 * j + 1, kb * Q, kb * Q + Q);
-          float p0 = FP8 ? __uint_as_float(v0) : float(int(v0));
-          float p1 = FP8 ? __uint_as_float(v1) : float(int(v1));
-          tot[j] = pack2(__float_as_uint(__fmaf_rn(p0, s, lane0(tot[j]))),
-                         __float_as_uint(__fmaf_rn(p1, s, lane1(tot[j]))));
-        }
-      }
-    } else {
-      if constexpr (PRESET) {
-        // fill every accumulator with the bias constant, then hand them to the MMA warp
-#pragma unroll
-        for (int i = 0; i < NBUF; ++i)
-#pragma unroll
-          for (int c = 0; c < CPT / 32; ++c)
-            tmem_st32_fill(taddr + uint32_t(i * Q + c0 + c * 32), I8_MAGIC_BITS);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (t.lane == 0)
-          for (int i = 0; i < NBUF; ++i) mbar_arrive(smem_u32(&t.ctrl->acc_empty[i]));
-      }
-      const unsigned long long neg_magic = pack2(__float_as_uint(-I8_MAGIC), __float_as_uint(-I8_MAGIC));
-#pragma unroll 1
-      for (int kb = 0; kb < g.num_kb; ++kb) {
-        const int buf = kb % NBUF;
-        const float s = block_scale(g, a, t, kb, mq, nq, kq);
-        const unsigned long long s2 = pack2(__float_as_uint(s), __float_as_uint(s));
-        ok = mbar_wait(smem_u32(&t.ctrl->acc_full[buf]), uint32_t(kb / NBUF) & 1u, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);  // keep the warp together for tcgen05.ld
-        if (!ok) break;
-        tc_fence_after();
-        const bool refill = PRESET && (kb + NBUF < g.num_kb);
-        // both 32-column loads of this thread's slice are in flight before the first wait
-        uint32_t v[CPT / 32][32];
-#pragma unroll
-        for (int c = 0; c < CPT / 32; ++c) tmem_ld32(taddr + uint32_t(buf * Q + c0 + c * 32), v[c]);
-        tmem_wait_ld();
-        if (refill) {
-#pragma unroll
-          for (int c = 0; c < CPT / 32; ++c)
-            tmem_st32_fill(taddr + uint32_t(buf * Q + c0 + c * 32), I8_MAGIC_BITS);
-        }
-#pragma unroll
-        for (int c = 0; c < CPT / 32; ++c) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            unsigned long long p = pack2(v[c][2 * j], v[c][2 * j + 1]);
-            if constexpr (PRESET) p = add2(p, neg_magic);  // exact: float(partial)
-            tot[c * 16 + j] = fma2(p, s2, tot[c * 16 + j]);
-          }
-        }
-        if (refill) tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (t.lane == 0) mbar_arrive(smem_u32(&t.ctrl->acc_empty[buf]));
-      }
-      if (!ok && t.lane == 0)
-        atomicCAS(g.status, 0u, unsigned(ST_EPILOGUE_TIMEOUT) | unsigned(blockIdx.x & 0xff));
-    }
     float vals[CPT];
 #pragma unroll
-    for (int j = 0; j < CPT / 2; ++j) { vals[2 * j] = lane0(tot[j]); vals[2 * j + 1] = lane1(tot[j]); }
-    // A warp that gave up still walks through the tail's barriers, without storing.
+    for (int j = 0; j < CPT; ++j) vals[j] = 0.f;
+#pragma unroll 1
+    for (int kb = 0; kb < g.num_kb; ++kb) {
+      const float s = block_scale(g, a, t, kb, mq, nq, kq);
+#pragma unroll 4
+      for (int j = 0; j < CPT; ++j) {
+        const uint32_t v = simt_dot<KIND, uint8_t>(g, t.b, t.row, t.col0 + c0 + j, kb * Q, kb * Q + Q);
+        const float p = FP8 ? __uint_as_float(v) : float(int(v));
+        vals[j] = __fmaf_rn(p, s, vals[j]);
+      }
+    }
     const Pre pre = tail_prefetch(g, a, t, mq, nq, kq);
-    tail(g, a, t, vals, ok, pre, mq, nq, kq);
+    tail(g, a, t, vals, true, pre, mq, nq, kq);
   }
 
   // What the tail needs from global memory besides the accumulator: the row diagonal,

@@ -88,7 +88,6 @@ struct EpiFloat {
   // K = 4096 alone would exceed the 1e-5 bar of this path.
   static constexpr int PROMOTE_KB = IS_F32 ? 1 : 0;
   static constexpr int NBUF = IS_F32 ? 2 : 1;
-  static constexpr bool PRESET = false;
   static constexpr int EPI_WARPS = 4;
   static constexpr int STAGES = 3;
   static constexpr int MIN_CTAS = IS_F32 ? 1 : 2;

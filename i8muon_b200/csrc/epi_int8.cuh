@@ -36,7 +36,6 @@ struct EpiI8 {
   static constexpr bool BLOCKQ = false;
   static constexpr int PROMOTE_KB = 0;
   static constexpr int NBUF = 1;
-  static constexpr bool PRESET = false;
   static constexpr int EPI_WARPS = 4;
   static constexpr int STAGES = 3;
   static constexpr int MIN_CTAS = 2;

@@ -12,12 +12,15 @@
 //
 // Measured facts behind the structure (B200, update GEMM 4096 x 14336, K = 4096):
 //   * every K block has its own accumulator, so K blocks are independent work items for
-//     the tensor core.  ONE issuing thread needs ~730 cycles of dependent instructions
-//     per K block (two barrier waits, descriptors, four MMAs, two commits) against 271
-//     cycles of MMA time; two producers and two issuers on alternate K blocks cut the
-//     floor of the pipeline from 0.37 to 0.25 us per K block;
-//   * the per-K-block scale products are staged in shared memory per tile;
-//   * one mbarrier arrival per epilogue warp, not per thread.
+//     the tensor core; two producers and two issuers work on alternate K blocks;
+//   * a 128-byte K block of a 128x128 tile moves 32 KB into shared memory and the four
+//     MMAs read 32 KB back: 512 cycles of shared-memory time against 256 cycles of tensor
+//     time, which is where the K loop sits (about 550 cycles per K block);
+//   * the epilogue loop is written for instruction count (see the step lambda): with the
+//     first, straightforward loop the kernel spent 800 cycles per K block, two to three
+//     bookkeeping instructions per useful one;
+//   * the per-K-block scale products are staged in shared memory per tile; one mbarrier
+//     arrival per epilogue warp, not per thread.
 #pragma once
 #include "epi_bq.cuh"
 

@@ -179,23 +179,21 @@ struct AccRegs {
 //   KIND, Elem, PARTS (operand planes per side: 1, or 2 for split-TF32),
 //   PROMOTE_KB (0: the whole K extent accumulates in tensor memory; n > 0: every n
 //   K blocks the partial accumulator is folded into FP32 registers by the epilogue
-//   warps while the tensor core fills the other TMEM buffer), BLOCKQ (the fold is
-//   the block-scaled promotion of run_blockq), STAGES, MIN_CTAS, IDESC, struct Args,
-//   static __device__ void run(g, args, t, acc)              (whole-K)
-//   static __device__ void run_blockq(g, args, t, tmem, ctrl) (per-K-block)
+//   warps while the tensor core fills the other TMEM buffer), BLOCKQ (block-quantised
+//   epilogue: only its debug core runs here), STAGES, MIN_CTAS, IDESC, struct Args,
+//   static __device__ void run(g, args, t, acc)   (whole-K and chunked promotion)
+//   static __device__ void run_debug(g, args, t)  (BLOCKQ)
 // DEBUG = true is the test-only core: no TMA / tcgen05, the epilogue threads compute
 // plain dot products.  It is a separate instantiation so that the product kernels
 // carry none of its code or register pressure.
-// Warp layout: warp 0 producer, warp 1 MMA issuer.  With four epilogue warps they are
-// warps 2..5.  With eight, the CTA is three warpgroups: warps 0..3 are the control
-// warpgroup (two of them idle) and shrink their register allotment, warps 4..11 are two
-// epilogue warpgroups that grow theirs (setmaxnreg), so that each epilogue thread can
-// hold its slice of the accumulator plus a full set of TMEM loads in flight.
+// Warp layout: warp 0 producer, warp 1 MMA issuer, then the epilogue warps: four of them
+// are warps 2..5; eight start at warp 4 so that every epilogue warp w reads the TMEM lane
+// quarter w % 4.  The block-quantised epilogues (eight warps) run in this skeleton only with
+// the debug core; their product kernel is bq_persistent_kernel.
 template <class Epi>
 struct WarpLayout {
-  static constexpr int EPI_WARP0 = Epi::EPI_WARPS == 8 ? 4 : 2;
+  static constexpr int EPI_WARP0 = Epi::EPI_WARPS > 4 ? 4 : 2;
   static constexpr int THREADS = 32 * (EPI_WARP0 + Epi::EPI_WARPS);
-  static constexpr bool REBALANCE = Epi::EPI_WARPS == 8;
 };
 
 template <class Epi, bool DEBUG>
@@ -248,8 +246,8 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t smem_base = smem_u32(smem);
   constexpr int EPI_WARP0 = WarpLayout<Epi>::EPI_WARP0;
 
+  static_assert(!Epi::BLOCKQ || DEBUG, "block-quantised GEMMs run in bq_persistent_kernel");
   if (warp < EPI_WARP0) {
-  if constexpr (WarpLayout<Epi>::REBALANCE) setmaxnreg_dec<56>();
   if (!DEBUG && warp == 0 && lane == 0) {
     // ------------------------------------------------------------ producer
     int issued = 0;
@@ -299,14 +297,9 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         chunk_first = (kb % PROMOTE) == 0;
         chunk_last = (kb % PROMOTE) == PROMOTE - 1 || kb == g.num_kb - 1;
         if (chunk_first) {
-          // PRESET: the epilogue warps hand over every buffer filled with the bias
-          // constant (completion 0 is the initial fill); otherwise a buffer is free
-          // until its first reuse.
-          if (Epi::PRESET) {
-            ok = mbar_wait(smem_u32(&ctrl->acc_empty[buf]), uint32_t(use) & 1u, abort_flag);
-          } else if (use >= 1) {
+          // a buffer is free until its first reuse
+          if (use >= 1)
             ok = mbar_wait(smem_u32(&ctrl->acc_empty[buf]), uint32_t(use - 1) & 1u, abort_flag);
-          }
           if (!ok) break;
         }
         d = tmem_base + uint32_t(buf * TILE);
@@ -321,7 +314,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // 32 bytes of K per instruction: advance the start address inside the
         // 128-byte swizzle row (address field is in 16-byte units).
         const uint64_t adv = uint64_t(ks * 2);
-        uint32_t accumulate = (!Epi::PRESET && chunk_first && ks == 0) ? 0u : 1u;
+        uint32_t accumulate = (chunk_first && ks == 0) ? 0u : 1u;
         umma<Epi::KIND>(d, adesc + adv, bdesc + adv, Epi::IDESC, accumulate);
         if constexpr (PARTS == 2) {
           // split-TF32: hi*hi (above) + hi*lo + lo*hi
@@ -346,7 +339,6 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   } else {
     // ------------------------------------------------------------ epilogue
-    if constexpr (WarpLayout<Epi>::REBALANCE) setmaxnreg_inc<224>();
     TileCtx t;
     t.b = b; t.tm = tm; t.tn = tn; t.row0 = row0; t.col0 = col0;
     t.q = warp & 3; t.lane = lane;
@@ -357,7 +349,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     t.red = ctrl->red; t.diag = ctrl->diag; t.tsm = nullptr;
     const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16);
     if constexpr (Epi::BLOCKQ) {
-      Epi::template run_blockq<DEBUG>(g, args, t, taddr, abort_flag);
+      Epi::run_debug(g, args, t);
     } else if constexpr (PROMOTE > 0) {
       if constexpr (DEBUG) {
         AccWholeK<Epi::KIND, typename Epi::Elem, true> acc{g, t, taddr};

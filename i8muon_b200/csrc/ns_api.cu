@@ -125,7 +125,10 @@ int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_
   } else {
     ma2 = ma; mb2 = mb;
   }
-  auto kernel = g_debug_simt ? ns_gemm_kernel<Epi, true> : ns_gemm_kernel<Epi, false>;
+  auto kernel = ns_gemm_kernel<Epi, true>;
+  if constexpr (!Epi::BLOCKQ) {
+    if (!g_debug_simt) kernel = ns_gemm_kernel<Epi, false>;
+  }
   CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
   kernel<<<dim3(unsigned(blocks)), WarpLayout<Epi>::THREADS, SMEM, stream>>>(ma, mb, ma2, mb2, g, args);
   LAUNCH_CHECK(name);
