@@ -14,7 +14,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent / "csrc"
 LIBRARY = CSRC / "libi8muon_b200.so"
 SOURCES = ("ns_api.cu",)
-HEADERS = ("ptx_sm100.cuh", "gemm_core.cuh", "gemm_bq_persistent.cuh", "epi_float.cuh", "epi_int8.cuh", "epi_bq.cuh",
+HEADERS = ("ptx_sm100.cuh", "gemm_core.cuh", "gemm_bq_persistent.cuh", "gemm_wholek_persistent.cuh", "epi_float.cuh", "epi_int8.cuh", "epi_bq.cuh",
            "passes.cuh")
 NVCC_FLAGS = (
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

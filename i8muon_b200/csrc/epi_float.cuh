@@ -217,7 +217,7 @@ struct EpiFloat {
       for (int c = 0; c < TILE / 32; ++c) body(c);
     } else {
 #pragma unroll 1
-      for (int c = 0; c < TILE / 32; ++c) body(c);
+      for (int c = t.c_begin; c < t.c_end; ++c) body(c);
     }
   }
 };

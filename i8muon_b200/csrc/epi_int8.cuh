@@ -59,7 +59,7 @@ struct EpiI8 {
     }
     if constexpr (MODE == I8_UPDATE || MODE == I8_UPDATE_FINAL) sb = a.b_scale[t.b];
 #pragma unroll 1
-    for (int c = 0; c < TILE / 32; ++c) {
+    for (int c = t.c_begin; c < t.c_end; ++c) {
       uint32_t v[32];
       acc.load(c, v);
       const int colb = t.col0 + c * 32;

@@ -75,6 +75,7 @@ struct TileCtx {
   int half;     // column slice of this warp when a row is split over several warps
   int ew;       // epilogue warp index (0 .. EPI_WARPS-1)
   int lane;
+  int c_begin, c_end;  // 32-column chunks of the tile row that this thread handles (whole-K epilogues)
   Ctrl* ctrl;
   float* red;   // shared scratch for the tile-wide reduction (one float per epilogue warp)
   float* diag;  // shared scratch: TILE floats
@@ -347,6 +348,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     t.row = row0 + t.r;
     t.ctrl = ctrl;
     t.red = ctrl->red; t.diag = ctrl->diag; t.tsm = nullptr;
+    t.c_begin = 0; t.c_end = TILE / 32;
     const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16);
     if constexpr (Epi::BLOCKQ) {
       Epi::run_debug(g, args, t);

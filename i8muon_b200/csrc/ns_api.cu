@@ -7,6 +7,7 @@
 #include "epi_float.cuh"
 #include "epi_int8.cuh"
 #include "gemm_bq_persistent.cuh"
+#include "gemm_wholek_persistent.cuh"
 #include "passes.cuh"
 
 #include <cstdarg>
@@ -23,6 +24,7 @@ namespace {
 
 thread_local char g_error[512] = "";
 int g_debug_simt = 0;
+int g_wholek_persistent = 1;   // 0: one CTA per tile (variant 1 of "wholek_gemm")
 int g_bq_variant = 0;   // 0: six-stage ring, 1: four-stage ring (chosen by the host-side tuner)
 std::atomic<unsigned long long> g_launches{0};
 
@@ -95,6 +97,8 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int esize, int k, int ro
 }
 
 // ------------------------------------------------------------ GEMM launch
+int sm_count();
+
 template <class Epi>
 int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_lo, int batch,
                 int m, int n, int k, int lm, int ln, int sym, unsigned* status,
@@ -124,6 +128,18 @@ int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_
     if (int rc = make_operand_map(&mb2, bt_lo, ES, k, n, batch)) return rc;
   } else {
     ma2 = ma; mb2 = mb;
+  }
+  // products that accumulate their whole K extent in tensor memory: persistent kernel
+  if constexpr (!Epi::BLOCKQ && Epi::PARTS == 1 && Epi::PROMOTE_KB == 0) {
+    if (!g_debug_simt && g_wholek_persistent) {
+      constexpr size_t PSMEM = size_t(WKP_STAGES) * 2 * TILE_BYTES + sizeof(Ctrl) + 1024;
+      auto pk = wholek_persistent_kernel<Epi>;
+      CUDA_TRY(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PSMEM)));
+      const unsigned grid = unsigned(std::min<long long>(blocks, sm_count()));
+      pk<<<grid, WKP_THREADS, PSMEM, stream>>>(ma, mb, g, args);
+      LAUNCH_CHECK(name);
+      return 0;
+    }
   }
   auto kernel = ns_gemm_kernel<Epi, true>;
   if constexpr (!Epi::BLOCKQ) {
@@ -239,13 +255,15 @@ extern "C" int i8m_set_debug_core(int simt) {
 }
 extern "C" int i8m_variant_count(const char* operation) {
   if (operation && std::strcmp(operation, "bq_gemm") == 0) return 2;
+  if (operation && std::strcmp(operation, "wholek_gemm") == 0) return 2;
   return 0;
 }
 extern "C" int i8m_set_variant(const char* operation, int variant) {
-  if (!operation || std::strcmp(operation, "bq_gemm") != 0)
+  if (!operation || (std::strcmp(operation, "bq_gemm") != 0 && std::strcmp(operation, "wholek_gemm") != 0))
     return fail(I8M_E_ARGUMENT, "set_variant: unknown operation");
-  if (variant < 0 || variant >= 2) return fail(I8M_E_ARGUMENT, "set_variant: bq_gemm has variants 0 and 1");
-  g_bq_variant = variant;
+  if (variant < 0 || variant >= 2) return fail(I8M_E_ARGUMENT, "set_variant: variants are 0 and 1");
+  if (operation[0] == 'b') g_bq_variant = variant;
+  else g_wholek_persistent = variant == 0 ? 1 : 0;
   return 0;
 }
 

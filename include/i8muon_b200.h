@@ -63,6 +63,8 @@ int i8m_set_debug_core(int simt);
 /* Kernel variants a host-side tuner can choose between, the counterpart of the tile ids
  * that the reference's KernelFactory times (src/i8muon/_cuda_factory.py:62-102).
  * operation "bq_gemm": 0 = six-stage operand ring (default), 1 = four-stage ring.
+ * operation "wholek_gemm" (FP16/BF16/global-INT8 products): 0 = persistent kernel, one CTA per
+ * SM (default), 1 = one CTA per output tile.
  * The choice is process-wide and applies to launches made after the call. */
 int i8m_variant_count(const char* operation);
 int i8m_set_variant(const char* operation, int variant);
