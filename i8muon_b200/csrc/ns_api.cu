@@ -611,6 +611,45 @@ extern "C" int i8m_apply(void* const* params, int count, const void* update, lon
   return 0;
 }
 
+// AdamW companion for the parameters outside Muon; FP32 moments, parameters and gradients in
+// any of the three floating types.  bias corrections are passed by the host (1 - beta^step).
+extern "C" int i8m_adamw(void* const* params, const void* const* grads, float* const* exp_avg,
+                         float* const* exp_avg_sq, const long long* numel, int count, int param_dtype,
+                         int grad_dtype, float lr, float beta1, float beta2, float eps,
+                         float weight_decay, float bias_correction1, float bias_correction2,
+                         i8m_stream_t stream) {
+  if (!params || !grads || !exp_avg || !exp_avg_sq || !numel || count < 1 || !float_dtype_ok(param_dtype) ||
+      !float_dtype_ok(grad_dtype) || !(bias_correction1 > 0.f) || !(bias_correction2 > 0.f))
+    return fail(I8M_E_ARGUMENT, "adamw: bad argument");
+  const float decay = 1.f - lr * weight_decay;
+  const float step_size = lr / bias_correction1;
+  const float inv_bc2_sqrt = 1.f / sqrtf(bias_correction2);
+  for (int first = 0; first < count; first += ADAM_MAX) {
+    const int c = std::min(ADAM_MAX, count - first);
+    AdamTable tab;
+    long long longest = 0;
+    for (int i = 0; i < c; ++i) {
+      const int k = first + i;
+      if (!params[k] || !grads[k] || !exp_avg[k] || !exp_avg_sq[k] || numel[k] < 1)
+        return fail(I8M_E_ARGUMENT, "adamw: null tensor or empty tensor");
+      tab.param[i] = params[k]; tab.grad[i] = grads[k];
+      tab.exp_avg[i] = exp_avg[k]; tab.exp_avg_sq[i] = exp_avg_sq[k];
+      tab.numel[i] = numel[k];
+      longest = std::max(longest, numel[k]);
+    }
+    dim3 grid(unsigned(std::min<long long>(cdiv(longest, 256 * 4), 148 * 16)), c);
+#define ADAM_LAUNCH(P)                                                                              \
+  DISPATCH_IN(grad_dtype, G, (adamw_kernel<P, G><<<grid, 256, 0, S(stream)>>>(tab, decay, beta1, beta2, eps, \
+                                                                              step_size, inv_bc2_sqrt)))
+    if (param_dtype == I8M_F32) ADAM_LAUNCH(float);
+    else if (param_dtype == I8M_F16) ADAM_LAUNCH(__half);
+    else ADAM_LAUNCH(__nv_bfloat16);
+#undef ADAM_LAUNCH
+    LAUNCH_CHECK("adamw");
+  }
+  return 0;
+}
+
 // ============================================== whole Newton-Schulz drivers
 namespace {
 

@@ -571,4 +571,44 @@ apply_kernel(ApplyTable tab, const U* update, long long numel, int decay_mode, f
   for (; i < numel; i += stride) p[i] = round_to<P>(one(widen<P>(p[i]), widen<U>(u[i])));
 }
 
+// ----------------------------------------------------------------- AdamW
+// Multi-tensor AdamW for the parameters Muon does not take (embeddings, heads, vectors):
+// up to ADAM_MAX tensors of different sizes per launch, FP32 moments, decoupled decay.
+// Per element, in this order (the statements of torch.optim.AdamW's single-tensor path):
+//   p  = p * (1 - lr * wd)
+//   m  = lerp(m, g, 1 - beta1);   v = beta2 * v + (1 - beta2) * g * g
+//   p -= (lr / bc1) * m / (sqrt(v) / sqrt(bc2) + eps)
+constexpr int ADAM_MAX = 24;
+struct AdamTable {
+  void* param[ADAM_MAX];
+  const void* grad[ADAM_MAX];
+  float* exp_avg[ADAM_MAX];
+  float* exp_avg_sq[ADAM_MAX];
+  long long numel[ADAM_MAX];
+};
+
+template <typename P, typename G>
+__global__ void __launch_bounds__(256)
+adamw_kernel(AdamTable tab, float decay, float beta1, float beta2, float eps, float step_size,
+             float inv_bc2_sqrt) {
+  const int t = blockIdx.y;
+  P* p = static_cast<P*>(tab.param[t]);
+  const G* g = static_cast<const G*>(tab.grad[t]);
+  float* m = tab.exp_avg[t];
+  float* v = tab.exp_avg_sq[t];
+  const long long n = tab.numel[t];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float gf = widen<G>(g[i]);
+    float pf = __fmul_rn(widen<P>(p[i]), decay);
+    const float mf = lerp_f(m[i], gf, 1.f - beta1);
+    const float vf = __fmaf_rn(__fmul_rn(gf, gf), 1.f - beta2, __fmul_rn(v[i], beta2));
+    m[i] = mf;
+    v[i] = vf;
+    const float denom = __fadd_rn(__fmul_rn(sqrtf(vf), inv_bc2_sqrt), eps);
+    pf = __fmaf_rn(-step_size, __fdiv_rn(mf, denom), pf);
+    p[i] = round_to<P>(pf);
+  }
+}
+
 }  // namespace i8m

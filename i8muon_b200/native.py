@@ -59,6 +59,8 @@ _SIGNATURES = {
                              c_float, c_int, _P]),
     "i8m_apply": (c_int, [POINTER(_P), c_int, _P, c_longlong, c_int, c_int, c_int, c_float,
                           c_float, _P]),
+    "i8m_adamw": (c_int, [POINTER(_P), POINTER(_P), POINTER(_P), POINTER(_P), POINTER(c_longlong), c_int,
+                          c_int, c_int, c_float, c_float, c_float, c_float, c_float, c_float, c_float, _P]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

@@ -184,6 +184,19 @@ int i8m_apply(void* const* params, int count, const void* update_device, long lo
               int param_dtype, int update_dtype, int decay_mode, float decay, float neg_lr,
               i8m_stream_t stream);
 
+/* AdamW for the parameters Muon does not take (embeddings, heads, vectors).  No counterpart in
+ * the reference: its `scalar_optimizer` slot takes any torch optimizer
+ * (src/i8muon/_optimizer.py:223,254-255); this is the fused companion for that slot.
+ * `count` tensors of possibly different sizes (numel[i]) as host arrays of device pointers;
+ * FP32 moments; decoupled decay.  Per element: p *= 1 - lr*weight_decay;
+ * m = lerp(m, g, 1-beta1); v = beta2*v + (1-beta2)*g*g;
+ * p -= lr/bias_correction1 * m / (sqrt(v)/sqrt(bias_correction2) + eps),
+ * with bias_correction_k = 1 - beta_k^step computed by the caller. */
+int i8m_adamw(void* const* params, const void* const* grads, float* const* exp_avg,
+              float* const* exp_avg_sq, const long long* numel, int count, int param_dtype,
+              int grad_dtype, float lr, float beta1, float beta2, float eps, float weight_decay,
+              float bias_correction1, float bias_correction2, i8m_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

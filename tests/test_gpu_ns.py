@@ -229,6 +229,28 @@ def test_baseline_config_shapes_reduced_batch(cuda_device):
     check_status()
 
 
+def test_benchmark_gate_projection_full_size(cuda_device):
+    """The largest matrix of the benchmark set, 14336 x 4096 (rows > cols: transposed on the way in
+    and out, 112 K blocks in the Gram product, 3584 update tiles), on the benchmark's route
+    (INT8-BQ after one FP16 iteration).  Size-independent properties: the result is close to the
+    FP32 iteration, its Gram matrix Y^T Y is near the identity band of the schedule, and the
+    same matrix inside a batch of two gives bit-identical output (tiles of a batch are independent)."""
+    engine = CutlassNSInt8()
+    x = make((1, 14336, 4096), torch.bfloat16, 21, std=1e-3)
+    y = engine._regular_bq(x.to(cuda_device), C5, 1e-7, True, "int8_bq")
+    check_status()
+    assert y.shape == x.shape and y.dtype == torch.bfloat16 and torch.isfinite(y).all()
+    truth = o.ns_fp32_torch(x, C5)
+    assert rel(y.float(), truth) < 0.12
+    gram = (y[0].float().mT @ y[0].float())            # 4096 x 4096, on the device
+    eig = torch.linalg.eigvalsh(gram.double())
+    assert 0.55 < float(eig.min()) and float(eig.max()) < 1.6   # sigma^2 of a schedule that ends in [0.75, 1.25]
+    pair = torch.cat([x, make((1, 14336, 4096), torch.bfloat16, 22, std=1e-3)]).to(cuda_device)
+    both = engine._regular_bq(pair, C5, 1e-7, True, "int8_bq")
+    check_status()
+    assert torch.equal(both[0], y[0])
+
+
 def test_autotuned_engine_and_kernel_variants_give_identical_results(cuda_device):
     """The tuner only chooses between schedules of the same arithmetic: the four-stage variant of
     the block-quantised GEMM, and an engine with autotune on, reproduce the default bit for bit."""

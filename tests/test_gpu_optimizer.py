@@ -223,3 +223,43 @@ def test_sharded_step_streams_host_gradients(cuda_device):
         assert torch.equal(a, b)
     for i in results[0][1]:
         assert torch.equal(results[0][1][i], results[1][1][i])
+
+
+@pytest.mark.parametrize("pdtype", [torch.float32, torch.bfloat16])
+def test_fused_adamw_matches_torch_adamw(cuda_device, pdtype):
+    """FusedAdamW (one multi-tensor launch) against torch.optim.AdamW's single-tensor statements in
+    FP32, on tensors of unequal, odd sizes over several steps; it also works in Muon's
+    scalar_optimizer slot.  BF16 parameters are held to one BF16 ulp of the FP32 trajectory."""
+    from i8muon_b200 import FusedAdamW
+    g = torch.Generator().manual_seed(5)
+    shapes = [(50257, 3), (7,), (1, 1025), (64,)] + [(33,)] * 30      # more than one table of 24
+    start = [torch.randn(s, generator=g) * 0.1 for s in shapes]
+    grads = [[torch.randn(s, generator=g) * 0.01 for s in shapes] for _ in range(4)]
+    kw = dict(lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ref_params = [p.clone().to(cuda_device).requires_grad_() for p in start]
+    ref = torch.optim.AdamW(ref_params, foreach=False, fused=False, **kw)
+    ours_params = [p.clone().to(pdtype).to(cuda_device).requires_grad_() for p in start]
+    ours = FusedAdamW(ours_params, **kw)
+    for step_grads in grads:
+        for p, q, gr in zip(ref_params, ours_params, step_grads):
+            p.grad = gr.to(cuda_device)
+            q.grad = gr.to(pdtype).to(cuda_device) if pdtype == torch.float32 else gr.to(cuda_device)
+        ref.step()
+        ours.step()
+    for p, q in zip(ref_params, ours_params):
+        if pdtype == torch.float32:
+            torch.testing.assert_close(q, p, rtol=2e-6, atol=2e-8)   # parameters are O(0.1): a few FP32 ulps
+        else:
+            # a BF16 parameter re-rounds after every step: allow the accumulated half-ulps
+            assert ((q.float() - p).abs() <= 4 * 2.0 ** -8 * p.abs() + 1e-6).all()
+    state = ours.state[ours_params[0]]
+    assert state["step"] == 4 and state["exp_avg"].dtype == torch.float32
+    # in Muon's scalar_optimizer slot
+    w = (torch.randn((64, 96), generator=g) * 0.02).to(cuda_device).requires_grad_()
+    v = torch.zeros(96, device=cuda_device, requires_grad=True)
+    opt = Muon([w], lr=0.02, scalar_optimizer=FusedAdamW([v], lr=1e-2))
+    w.grad = torch.randn_like(w) * 1e-3
+    v.grad = torch.ones_like(v)
+    opt.step()
+    check_status()
+    assert torch.all(v < 0) and len(opt.param_groups) == 2

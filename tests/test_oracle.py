@@ -119,3 +119,21 @@ def test_step_arithmetic_matches_reference_muon_step(host_golden, step_golden):
                            weight_decay=case["wd"], weight_decay_mode=case["mode"])
             assert torch.equal(p, step_golden[f"{key}.param{s + 1}"]), key
             assert torch.equal(b, step_golden[f"{key}.buf{s + 1}"]), key
+
+
+def test_adamw_restatement_follows_torch_adamw():
+    """The AdamW statements used by the fused companion kernel, against torch.optim.AdamW on CPU."""
+    g = torch.Generator().manual_seed(3)
+    p0 = torch.randn(257, generator=g) * 0.1
+    grads = [torch.randn(257, generator=g) * 0.01 for _ in range(5)]
+    kw = dict(lr=3e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    ref = p0.clone().requires_grad_()
+    opt = torch.optim.AdamW([ref], foreach=False, **kw)
+    p = p0.numpy().copy()
+    m, v = np.zeros_like(p), np.zeros_like(p)
+    for step, gr in enumerate(grads, 1):
+        ref.grad = gr.clone()
+        opt.step()
+        p = o.adamw_update(p, gr.numpy(), m, v, step, **kw)
+    np.testing.assert_allclose(p, ref.detach().numpy(), rtol=2e-6, atol=2e-8)
+    np.testing.assert_allclose(m, opt.state[ref]["exp_avg"].numpy(), rtol=2e-6, atol=1e-10)
