@@ -87,7 +87,7 @@ class CutlassNSInt8:
         return hit
 
     # ------------------------------------------------------------- launch
-    def _run(self, route, x, coeffs, eps, compute, alignment, spec_precision, fp16_first):
+    def _run(self, route, x, coeffs, eps, compute, alignment, spec_precision, fp16_first, out=None):
         coeffs = DEFAULT_COEFFICIENTS if coeffs is None else coeffs
         shape = x.shape
         batch, rows, cols, *_ = matrix_spec(tuple(shape), x.dtype, x.device, spec_precision, alignment)
@@ -99,7 +99,11 @@ class CutlassNSInt8:
             raise ValueError("I8MUON_GRAM_RESET must be a binary string starting with 0")
         with torch.cuda.device(x.device):
             size = native.ns_workspace_bytes(route, batch, rows, cols, dtype, compute, steps, fp16_first)
-            out = torch.empty_like(x)
+            if out is None:
+                out = torch.empty_like(x)
+            elif (out.shape != x.shape or out.dtype != x.dtype or out.device != x.device
+                  or not out.is_contiguous() or out.data_ptr() == x.data_ptr()):
+                raise ValueError("out must be a contiguous tensor like x that does not alias it")
 
             def launch(variant):
                 native.call("i8m_set_variant", b"bq_gemm", int(variant))
@@ -117,35 +121,37 @@ class CutlassNSInt8:
         # The workspace may be reused by later allocations on this stream only.
         return out.view(shape)
 
-    def _regular_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16"):
+    # Every entry point takes the reference's arguments plus a keyword-only ``out``: a caller-owned
+    # tensor for the result (the sharded step lets NS write straight into its gather buffer).
+    def _regular_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16", *, out=None):
         """FP32 / BF16 / FP16 regular NS (src/i8muon/_cutlass_prec.py:90-106)."""
         precision = normalize_precision(precision)
         if precision not in _COMPUTE_CODES:
             raise ValueError(f"Unsupported floating-point precision: {precision}")
-        return self._run(native.ROUTE_FLOAT, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False)
+        return self._run(native.ROUTE_FLOAT, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False, out)
 
-    def _gram_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16"):
+    def _gram_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16", *, out=None):
         """Gram-space NS with restarts given by I8MUON_GRAM_RESET (src/i8muon/_cutlass_prec.py:107-130)."""
         precision = normalize_precision(precision)
         if precision not in _COMPUTE_CODES:
             raise ValueError(f"Unsupported floating-point precision: {precision}")
-        return self._run(native.ROUTE_GRAM, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False)
+        return self._run(native.ROUTE_GRAM, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False, out)
 
-    def _regular_i8(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="int8", *, block=False):
+    def _regular_i8(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="int8", *, block=False, out=None):
         """Global-scale INT8 NS, optionally after one FP16 iteration (src/i8muon/_cutlass.py:130-142)."""
         if block:
-            return self._run(native.ROUTE_BQ_INT8, x, coeffs, eps, native.F16, 128, "int8", self.fp16_first)
-        return self._run(native.ROUTE_INT8, x, coeffs, eps, native.F16, 16, "int8", self.fp16_first)
+            return self._run(native.ROUTE_BQ_INT8, x, coeffs, eps, native.F16, 128, "int8", self.fp16_first, out)
+        return self._run(native.ROUTE_INT8, x, coeffs, eps, native.F16, 16, "int8", self.fp16_first, out)
 
-    def _regular_bq(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float8_e4m3fn"):
+    def _regular_bq(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float8_e4m3fn", *, out=None):
         """128x128 block-quantised NS: INT8 honours fp16_first, E4M3 never does
         (src/i8muon/_cutlass.py:71-76)."""
         precision = normalize_precision(precision)
         if precision in ("int8_bq", "int8"):
-            return self._regular_i8(x, coeffs, eps, deterministic, "int8", block=True)
+            return self._regular_i8(x, coeffs, eps, deterministic, "int8", block=True, out=out)
         if precision != "float8_e4m3fn":
             raise ValueError(f"Unsupported block-quantised precision: {precision}")
-        return self._run(native.ROUTE_BQ_FP8, x, coeffs, eps, native.F16, 128, precision, False)
+        return self._run(native.ROUTE_BQ_FP8, x, coeffs, eps, native.F16, 128, precision, False, out)
 
 
 __all__ = ["CutlassNSInt8", "check_status", "status_word"]

@@ -390,9 +390,9 @@ def native_step_ops(ns_engine: CutlassNSInt8, *, lr, weight_decay, momentum, ns_
                     grads[0].numel(), native.torch_dtype_code(out.dtype), 1.0 - mu2, mu, int(nesterov),
                     torch.cuda.current_stream().cuda_stream)
 
-    def do_ns(x):
+    def do_ns(x, out=None):
         fn, actual = ns_engine.router(x.shape[-2], x.shape[-1], precision, use_gram, gram_aspect_threshold)
-        return fn(x, coeffs=ns_coefficients, eps=eps, deterministic=True, precision=actual)
+        return fn(x, coeffs=ns_coefficients, eps=eps, deterministic=True, precision=actual, out=out)
 
     def do_apply(params, updates):
         shape = params[0].shape

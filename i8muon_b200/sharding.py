@@ -20,6 +20,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Sequence, Tuple
 
+import inspect
+
 import torch
 import torch.distributed as dist
 
@@ -91,7 +93,9 @@ def build_plan(shapes: Sequence[Sequence[int]], keys: Sequence[Tuple], world: in
 @dataclass
 class StepOps:
     """momentum(grads, bufs, out): write stacked updates of len(grads) matrices into out[:len(grads)].
-    orthogonalise(x) -> same shape.  apply(params, updates): updates is (len(params), *shape)."""
+    orthogonalise(x) -> same shape; if it takes ``out=``, the result is written there (the step
+    then lets it write straight into the gather buffer and gathers in place).
+    apply(params, updates): updates is (len(params), *shape)."""
     momentum: Callable
     orthogonalise: Callable
     apply: Callable
@@ -115,6 +119,7 @@ class ShardedMuonStep:
         self.max_group_bytes = max_group_bytes
         self._staging: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._copy_stream = None
+        self._ns_takes_out = "out" in inspect.signature(ops.orthogonalise).parameters
         self._consumed: Dict[int, object] = {}   # chunk -> event: its gradients were read
 
     def _buffers_for(self, g: ShardGroup, width: int, like: torch.Tensor, parity: int):
@@ -186,9 +191,16 @@ class ShardedMuonStep:
                     consumed = torch.cuda.Event()
                     consumed.record(torch.cuda.current_stream(like.device))
                     self._consumed[c] = consumed
-                send[:len(mine)].copy_(self.ops.orthogonalise(send[:len(mine)]))
+                if self._ns_takes_out:
+                    own = recv[self.rank * width:self.rank * width + len(mine)]
+                    self.ops.orthogonalise(send[:len(mine)], out=own)
+                else:
+                    send[:len(mine)].copy_(self.ops.orthogonalise(send[:len(mine)]))
             if self.world > 1:
-                work = dist.all_gather_into_tensor(recv, send, group=self.group, async_op=True)
+                source = recv[self.rank * width:(self.rank + 1) * width] if self._ns_takes_out else send
+                work = dist.all_gather_into_tensor(recv, source, group=self.group, async_op=True)
+            elif self._ns_takes_out:
+                work = None
             else:
                 work, recv = None, send
             pending.append((g, first, width, recv, work))
