@@ -90,8 +90,17 @@ def worker(rank, world, store_path, result_path):
         stepper = ShardedMuonStep(params, steps=5, ops=ops, max_group_bytes=2 * 24 * 40 * 2)
         owned = set(stepper.plan.owned(rank))
         buffers = {i: bufs[i] for i in owned}
-        for step_grads in grads:
-            stepper.step(params, step_grads, buffers)
+        landing = [torch.zeros_like(g) for g in grads[0]]
+        for n, step_grads in enumerate(grads):
+            if n % 2 == 0:
+                stepper.step(params, step_grads, buffers)
+            else:
+                # gradients handed over as host tensors: only the owned ones are copied in
+                for t in landing:
+                    t.fill_(float("nan"))
+                stepper.step(params, landing, buffers, host_grads=step_grads)
+                assert all(torch.equal(landing[i], step_grads[i]) for i in owned)
+                assert all(torch.isnan(landing[i]).all() for i in range(len(landing)) if i not in owned)
         torch.save(dict(params=params, owned=sorted(owned), bufs={i: bufs[i] for i in owned}),
                    f"{result_path}.{rank}")
     finally:
