@@ -87,6 +87,15 @@ def build_plan(shapes: Sequence[Sequence[int]], keys: Sequence[Tuple], world: in
         g.slots = [[i for i in members if owner[i] == r] for r in range(world)]
         g.width = max(len(s) for s in g.slots)
         groups.append(g)
+    # The gather and the update of the last group have nothing to hide behind: take the groups in
+    # order of decreasing bytes per rank so that the cheapest one comes last (stable, and the same
+    # on every rank).
+    def exposed(g: ShardGroup) -> int:
+        numel = 1
+        for d in shapes[g.members[0]]:
+            numel *= int(d)
+        return g.width * numel
+    groups.sort(key=exposed, reverse=True)
     return ShardPlan(world=world, groups=groups, load=load)
 
 
