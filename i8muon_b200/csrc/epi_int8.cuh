@@ -25,6 +25,8 @@ struct I8Args {
   const float* diag;      // (batch, m): dG (square) or dP (update)
   const int8_t* row_b;    // update: A8 (batch, m, n) row-major
   float alpha, beta;      // square: b and c coefficients
+  float gain;             // update: multiplies b_scale when use_gain (completed-square / cubic rows)
+  int use_gain;
   int out_dtype, transpose;
 };
 
@@ -57,7 +59,10 @@ struct EpiI8 {
       sq = __fmul_rn(__fmul_rn(sa, sa), a.beta);
       ri = __fmul_rn(__fadd_rn(__fmul_rn(drow, a.beta), a.alpha), sa);
     }
-    if constexpr (MODE == I8_UPDATE || MODE == I8_UPDATE_FINAL) sb = a.b_scale[t.b];
+    if constexpr (MODE == I8_UPDATE || MODE == I8_UPDATE_FINAL) {
+      sb = a.b_scale[t.b];
+      if (a.use_gain) sb = __fmul_rn(sb, a.gain);   // int8.cu:258
+    }
 #pragma unroll 1
     for (int c = t.c_begin; c < t.c_end; ++c) {
       uint32_t v[32];

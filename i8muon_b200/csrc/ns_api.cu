@@ -425,6 +425,8 @@ extern "C" int i8m_i8_gemm(int mode, const int8_t* a, const int8_t* b_t, const i
   I8Args g;
   g.out = out; g.maximum = maximum; g.a_scale = a_scale; g.b_scale = b_scale; g.diag = diag;
   g.row_b = row_b; g.alpha = alpha; g.beta = beta; g.out_dtype = out_dtype; g.transpose = transpose;
+  g.gain = alpha; g.use_gain = mode == 4;
+  if (mode == 4) mode = 2;   // update whose right-hand scale is multiplied by alpha
   if (mode == 0) {
     if (!maximum) return fail(I8M_E_ARGUMENT, "i8_gemm: gram needs a maximum slot");
     return launch_gemm<EpiI8<I8_GRAM>>(a, nullptr, b_t, nullptr, batch, m, n, k, lm, ln, 1, status, g,
@@ -669,6 +671,7 @@ struct Bump {
 
 struct NsCall {
   int route, dtype, batch, rows, cols, compute, steps, fp16_first;
+  int factored = 0;   // coefficient rows are (c, p, q) of c * ((G + p I)^2 + q I)
   const void* x;
   void* out;
   const double* coeffs;
@@ -692,7 +695,8 @@ FMat take_fmat(Bump& ws, size_t elems, int compute) {
 
 // floating NS (regular and Gram); with plan == true only the workspace is sized.
 int run_float(const NsCall& c, Bump& ws, bool plan, bool gram, const void* x, void* out,
-              int out_dtype, int steps, const double* coeffs, int compute, bool normalize_input) {
+              int out_dtype, int steps, const double* coeffs, int compute, bool normalize_input,
+              bool factored = false) {
   const int B = c.batch, rows = c.rows, cols = c.cols;
   const int l = std::min(rows, cols), h = std::max(rows, cols);
   const int lp = pad_to(l, 16), hp = pad_to(h, 16);
@@ -725,8 +729,20 @@ int run_float(const NsCall& c, Bump& ws, bool plan, bool gram, const void* x, vo
   const FMat none;
   if (!gram) {
     for (int it = 0; it < steps; ++it) {
-      const double ca = coeffs[3 * it], cb = coeffs[3 * it + 1], cc = coeffs[3 * it + 2];
+      double ca = coeffs[3 * it], cb = coeffs[3 * it + 1], cc = coeffs[3 * it + 2];
       if (int rc = gemm(a, a, r, none, 0, lp, hp, l, 1, 0, 0, nullptr, 0, 0, 0)) return rc;
+      if (factored) {
+        // completed-square row (c, p, q): shift the Gram diagonal by p, then c*q I + c R'^2
+        // (src/i8muon/_cutlass_prec.py:97-100); 16-bit compute types only
+        const double fc = ca, fp = cb, fq = cc;
+        const long long n = (long long)B * l;
+        if (compute == I8M_F16)
+          diag_add_kernel<__half><<<unsigned(cdiv(n, 256)), 256, 0, c.stream>>>(static_cast<__half*>(r.p), B, lp, l, float(fp));
+        else
+          diag_add_kernel<__nv_bfloat16><<<unsigned(cdiv(n, 256)), 256, 0, c.stream>>>(static_cast<__nv_bfloat16*>(r.p), B, lp, l, float(fp));
+        LAUNCH_CHECK("diag_add");
+        ca = fc * fq; cb = 0.0; cc = fc;
+      }
       if (int rc = gemm(r, r, q0, none, 1, lp, lp, l, 1, 0, 0, nullptr, ca, cb, cc)) return rc;
       const bool final = it == steps - 1;
       if (int rc = gemm(q0, at, y, yt, 0, hp, lp, h, 0, final, final && transpose, out, 0, 0, 0)) return rc;
@@ -769,7 +785,7 @@ int run_float(const NsCall& c, Bump& ws, bool plan, bool gram, const void* x, vo
 
 // global-scale INT8 NS (src/i8muon/_cutlass.py:162-251)
 int run_int8(const NsCall& c, Bump& ws, bool plan, const void* x, int steps, const double* coeffs,
-             bool normalize_input) {
+             bool normalize_input, bool factored = false) {
   const int B = c.batch, rows = c.rows, cols = c.cols;
   const int l = std::min(rows, cols), h = std::max(rows, cols);
   const int lp = pad_to(l, 16), hp = pad_to(h, 16);
@@ -802,14 +818,20 @@ int run_int8(const NsCall& c, Bump& ws, bool plan, const void* x, int steps, con
                                rows, cols, lp, hp, transpose, c.eps, c.stream))
     return rc;
   for (int it = 0; it < steps; ++it) {
-    const float ca = float(coeffs[3 * it]), cb = float(coeffs[3 * it + 1]), cc = float(coeffs[3 * it + 2]);
+    // A completed-square row (c, p, q) is the same five stages with the Gram diagonal shifted
+    // by p, the polynomial G'^2 + q I (b = 0, c = 1, a = q: bit-identical expressions to the
+    // reference's unscaled modes) and c folded into the update's right-hand scale
+    // (src/i8muon/_cutlass.py:196-246).
+    float ca = float(coeffs[3 * it]), cb = float(coeffs[3 * it + 1]), cc = float(coeffs[3 * it + 2]);
+    float shift = 0.f, gain = 0.f;
+    if (factored) { gain = ca; shift = cb; ca = cc; cb = 0.f; cc = 1.f; }
     float* gmax = maxima + size_t(3 * it) * B;
     float* pmax = gmax + B;
     float* ymax = pmax + B;
     if (int rc = i8m_i8_gemm(0, a8, a8, nullptr, work, gmax, nullptr, nullptr, nullptr, B, lp, lp, hp, l,
                              l, 0, 0, 0, 0, 0, c.status, c.stream))
       return rc;
-    if (int rc = i8m_symmetric_quant(work, gmax, a_scale, nullptr, s8, g_scale, g_diag, B, lp, 0, 0, 0, 0, c.stream))
+    if (int rc = i8m_symmetric_quant(work, gmax, a_scale, nullptr, s8, g_scale, g_diag, B, lp, 0, shift, 0, 0, c.stream))
       return rc;
     if (int rc = i8m_i8_gemm(1, s8, s8, nullptr, work, pmax, g_scale, nullptr, g_diag, B, lp, lp, lp, l, l,
                              cb, cc, 0, 0, 0, c.status, c.stream))
@@ -817,8 +839,8 @@ int run_int8(const NsCall& c, Bump& ws, bool plan, const void* x, int steps, con
     if (int rc = i8m_symmetric_quant(work, pmax, g_scale, g_diag, s8, p_scale, p_diag, B, lp, 1, ca, cb, cc, c.stream))
       return rc;
     const bool final = it == steps - 1;
-    if (int rc = i8m_i8_gemm(2, s8, a8t, a8, final ? c.out : static_cast<void*>(work), ymax, p_scale,
-                             a_scale, p_diag, B, lp, hp, lp, l, h, 0, 0, final, transpose, c.dtype,
+    if (int rc = i8m_i8_gemm(factored ? 4 : 2, s8, a8t, a8, final ? c.out : static_cast<void*>(work), ymax, p_scale,
+                             a_scale, p_diag, B, lp, hp, lp, l, h, gain, 0, final, transpose, c.dtype,
                              c.status, c.stream))
       return rc;
     if (!final)
@@ -888,6 +910,20 @@ int ns_dispatch(const NsCall& c, Bump& ws, bool plan) {
       if (!float_dtype_ok(c.compute)) return fail(I8M_E_ARGUMENT, "bad compute dtype %d", c.compute);
       return run_float(c, ws, plan, c.route == I8M_ROUTE_GRAM, c.x, c.out, c.dtype, c.steps, c.coeffs,
                        c.compute, true);
+    case I8M_ROUTE_INT8_FACTORED: {
+      // completed-square rows (c, p, q), src/i8muon/_cutlass.py:93-128
+      if (!c.fp16_first) return run_int8(c, ws, plan, c.x, c.steps, c.coeffs, true, true);
+      if (c.steps == 1)
+        return run_float(c, ws, plan, false, c.x, c.out, c.dtype, 1, c.coeffs, I8M_F16, true, true);
+      void* first = ws.take(size_t(c.batch) * c.rows * c.cols * dtype_size(c.dtype));
+      size_t mark = ws.used;
+      if (int rc = run_float(c, ws, plan, false, c.x, first, c.dtype, 1, c.coeffs, I8M_F16, true, true)) return rc;
+      size_t after_float = ws.used;
+      ws.used = mark;
+      int rc = run_int8(c, ws, plan, first, c.steps - 1, plan ? nullptr : c.coeffs + 3, false, true);
+      ws.used = std::max(ws.used, after_float);
+      return rc;
+    }
     case I8M_ROUTE_INT8:
     case I8M_ROUTE_BQ_INT8: {
       const bool bq = c.route == I8M_ROUTE_BQ_INT8;

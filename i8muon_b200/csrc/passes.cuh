@@ -353,7 +353,8 @@ symmetric_quant_kernel(const In* input, const void* maximum, const float* orig_s
         diag[size_t(b) * m + row] =
             __fadd_rn(__fadd_rn(v, __fmul_rn(__fadd_rn(__fmul_rn(c2, d), c1), d)), c0);
       } else {
-        diag[size_t(b) * m + row] = __fmul_rn(v, sa);
+        // c0 shifts the Gram diagonal (completed-square rows, int8.cu:396); it is 0 otherwise
+        diag[size_t(b) * m + row] = __fadd_rn(__fmul_rn(v, sa), c0);
       }
     }
     tile[r][tx] = q;
@@ -373,6 +374,18 @@ symmetric_quant_kernel(const In* input, const void* maximum, const float* orig_s
       if (row < m && col < m) output[(size_t(b) * m + row) * m + col] = tile[tx][r];
     }
   }
+}
+
+// R[i][i] <- E(R[i][i] + shift) on every matrix of the batch: the diagonal shift of a
+// completed-square row in the floating first iteration (src/i8muon/_cutlass_prec.py:97-99).
+template <typename E>
+__global__ void __launch_bounds__(256)
+diag_add_kernel(E* r, int batch, int m, int logical, float shift) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)batch * logical) return;
+  const int b = int(i / logical), d = int(i - (long long)b * logical);
+  E* e = r + (size_t(b) * m + d) * m + d;
+  *e = round_to<E>(__fadd_rn(widen<E>(*e), shift));
 }
 
 // ----------------------------------------------------------- output quant

@@ -19,6 +19,7 @@ Differences that a caller can observe:
 from __future__ import annotations
 
 import ctypes
+import math
 import os
 from functools import lru_cache
 
@@ -142,6 +143,29 @@ class CutlassNSInt8:
         if block:
             return self._run(native.ROUTE_BQ_INT8, x, coeffs, eps, native.F16, 128, "int8", self.fp16_first, out)
         return self._run(native.ROUTE_INT8, x, coeffs, eps, native.F16, 16, "int8", self.fp16_first, out)
+
+    # ------------------------------------------------ opt-in polynomial entry points
+    def _regular_i8_factored(self, X, factor_rows, eps=1e-7, deterministic=True, *, out=None):
+        """Completed-square rows ``(c, p, q)``: X <- c * ((G + p I)^2 + q I) X per row, all in the
+        global-INT8 stages (the first row in FP16 when ``fp16_first``); src/i8muon/_cutlass.py:93-128."""
+        factors = tuple(tuple(float(v) for v in row) for row in factor_rows)
+        if not factors or any(len(row) != 3 or not all(map(math.isfinite, row)) for row in factors):
+            raise ValueError("Expected nonempty finite (c,p,q) factor rows")
+        return self._run(native.ROUTE_INT8_FACTORED, X, factors, eps, native.F16, 16, "int8", self.fp16_first, out)
+
+    def _regular_i8_grouped_cubic(self, X, input_gain, cubic_gains, terminal_abc, eps=1e-7):
+        """All-INT8 grouped cubics T <- -gain * (T T^T - I) T followed by one quintic; ignores
+        ``fp16_first`` (src/i8muon/_cutlass.py:78-84, _cutlass_cubic.py:8-71)."""
+        from .polynomial import grouped_cubic
+        return grouped_cubic(self, X, input_gain, cubic_gains, terminal_abc, eps)
+
+    def _regular_i8_cubic_abc(self, X, coeffs, eps=1e-7, deterministic=True, precision="int8"):
+        """Saved cubic rows ``(a, b, 0)`` with a > 0 > b, then one terminal quintic row; all INT8
+        (src/i8muon/_cutlass.py:86-91, _cutlass_cubic.py:74-87)."""
+        if precision != "int8":
+            raise ValueError("Cubic ABC evaluation requires INT8")
+        from .polynomial import cubic_abc
+        return cubic_abc(self, X, coeffs, eps)
 
     def _regular_bq(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float8_e4m3fn", *, out=None):
         """128x128 block-quantised NS: INT8 honours fp16_first, E4M3 never does

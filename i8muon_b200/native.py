@@ -15,7 +15,7 @@ from functools import lru_cache
 from .build import LIBRARY
 
 F32, F16, BF16 = 0, 1, 2
-ROUTE_FLOAT, ROUTE_GRAM, ROUTE_INT8, ROUTE_BQ_INT8, ROUTE_BQ_FP8 = range(5)
+ROUTE_FLOAT, ROUTE_GRAM, ROUTE_INT8, ROUTE_BQ_INT8, ROUTE_BQ_FP8, ROUTE_INT8_FACTORED = range(6)
 
 
 class NativeError(RuntimeError):

@@ -45,7 +45,9 @@ enum i8m_route {
   I8M_ROUTE_GRAM = 1,    /* _gram_prec     */
   I8M_ROUTE_INT8 = 2,    /* _regular_i8    */
   I8M_ROUTE_BQ_INT8 = 3, /* _regular_bq, int8 blocks */
-  I8M_ROUTE_BQ_FP8 = 4   /* _regular_bq, E4M3 blocks */
+  I8M_ROUTE_BQ_FP8 = 4,  /* _regular_bq, E4M3 blocks */
+  I8M_ROUTE_INT8_FACTORED = 5 /* _regular_i8_factored: coefficient rows are (c, p, q) of
+                                 c * ((G + p I)^2 + q I), src/i8muon/_cutlass.py:93-128 */
 };
 
 /* ---- library state ------------------------------------------------------ */
@@ -125,12 +127,14 @@ int i8m_input_quant(const void* x_device, int in_dtype, const float* amax_device
 /* aat / square / update: src/i8muon/csrc/int8.cu:529-537, 539-556, 592-627.
  * mode 0: out int32 (lower tiles), maximum int32[batch];
  * mode 1: out fp32, maximum fp32[batch], alpha = b, beta = c coefficient;
- * mode 2: out fp32 + maximum, or (final) the user's tensor in out_dtype. */
+ * mode 2: out fp32 + maximum, or (final) the user's tensor in out_dtype;
+ * mode 4: mode 2 with b_scale multiplied by alpha (factored_update, int8.cu:258, 606-627). */
 int i8m_i8_gemm(int mode, const int8_t* a, const int8_t* b_t, const int8_t* row_b, void* out,
                 void* maximum, const float* a_scale, const float* b_scale, const float* diag,
                 int batch, int m, int n, int k, int lm, int ln, float alpha, float beta, int final,
                 int transpose, int out_dtype, uint32_t* status_device, i8m_stream_t stream);
-/* symmetric_quant: src/i8muon/csrc/int8.cu:558-585 (quad 0: int32 Gram in, quad 1: fp32 polynomial in) */
+/* symmetric_quant: src/i8muon/csrc/int8.cu:558-585 (quad 0: int32 Gram in, c0 is added to the FP32
+ * diagonal - the shift of factored_quant, int8.cu:396, 0 otherwise; quad 1: fp32 polynomial in) */
 int i8m_symmetric_quant(const void* input, const void* maximum, const float* orig_scale,
                         const float* orig_diag, int8_t* output, float* scale, float* diag,
                         int batch, int m, int quad, float c0, float c1, float c2,

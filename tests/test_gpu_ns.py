@@ -281,3 +281,61 @@ def test_autotuned_engine_and_kernel_variants_give_identical_results(cuda_device
     assert set(scores) == {0, 1} and all(v > 0 for v in scores.values())
     with pytest.raises(native.NativeError):
         native.call("i8m_set_variant", b"no_such_op", 0)
+
+
+# completed squares of the first three rows of the default schedule: a + b g + c g^2 = c((g + p)^2 + q)
+FACTOR_ROWS = [(c, b / (2 * c), a / c - (b / (2 * c)) ** 2) for a, b, c in C5[:3]]
+
+
+@pytest.mark.parametrize("fp16_first", [True, False])
+@pytest.mark.parametrize("shape,dtype", [((2, 144, 400), torch.float32), ((1, 400, 144), torch.bfloat16)])
+def test_factored_int8_rows(cuda_device, fp16_first, shape, dtype):
+    """Opt-in completed-square rows c((G + pI)^2 + qI): with the kernel's own norm (and FP16 first
+    row) fed to the oracle the integer stages are bit-exact, so outputs agree to the final cast; the
+    result is also the expanded quintic (c(p^2+q), 2cp, c) up to quantisation noise."""
+    x = make(shape, dtype, 31, std=1e-3, outliers=True)
+    engine = CutlassNSInt8(fp16_first=fp16_first)
+    y = engine._regular_i8_factored(x.to(cuda_device), FACTOR_ROWS)
+    check_status()
+    assert y.shape == x.shape and y.dtype == x.dtype
+    first = None
+    if fp16_first:
+        first = engine._regular_i8_factored(x.to(cuda_device), FACTOR_ROWS[:1]).cpu()
+        ref_first = o.ns_float(x, FACTOR_ROWS[:1], 1e-7, "float16", norm=kernel_norm(x, cuda_device), factored=True)
+        assert rel(first, ref_first) < 2e-2
+    ref = o.ns_int8(x, FACTOR_ROWS, 1e-7, fp16_first=fp16_first, norm=kernel_norm(x, cuda_device), first=first,
+                    factored=True)
+    assert rel(y, ref) < 1e-6
+    # the same polynomial as the first three rows of the schedule, up to quantisation noise
+    truth = o.ns_fp32_torch(x, C5[:3])
+    independent = o.ns_int8(x, FACTOR_ROWS, 1e-7, fp16_first=fp16_first, factored=True)
+    assert rel(y.float(), truth) < 1.25 * rel(independent.float(), truth) + 1e-3
+    with pytest.raises(ValueError):
+        engine._regular_i8_factored(x.to(cuda_device), [(1.0, float("nan"), 0.0)])
+
+
+def test_grouped_cubic_and_cubic_abc(cuda_device):
+    """All-INT8 grouped cubics with a terminal quintic against the oracle fed the kernel's norm, and
+    the saved-ABC form, which is the same evaluation with shifts a/b and gains -b."""
+    engine = CutlassNSInt8()
+    abc = (3.4445, -4.775, 2.0315)
+    for shape, dtype in (((2, 144, 400), torch.float32), ((1, 400, 144), torch.bfloat16)):
+        x = make(shape, dtype, 37, std=1e-3, outliers=True)
+        y = engine._regular_i8_grouped_cubic(x.to(cuda_device), 1.1, [1.5, 1.4], abc)
+        check_status()
+        assert y.shape == x.shape and y.dtype == x.dtype
+        ref = o.ns_int8_grouped_cubic(x, 1.1, [1.5, 1.4], abc, norm=kernel_norm(x, cuda_device))
+        # bit-exact integer stages; a BF16 result may differ in single elements that sit on a rounding
+        # boundary of the final cast (one flipped element of 57 600 is 1.6e-5)
+        tol = 1e-6 if dtype == torch.float32 else 3e-5
+        assert rel(y, ref) < tol
+        rows = [(1.5, -1.5, 0.0), (1.4, -1.4, 0.0), abc]      # (a I + b G) X = b (G + a/b I) X
+        z = engine._regular_i8_cubic_abc(x.to(cuda_device), rows)
+        check_status()
+        same = o.ns_int8_grouped_cubic(x, 1.0, [1.5, 1.4], abc, diagonal_shifts=[-1.0, -1.0],
+                                       norm=kernel_norm(x, cuda_device))
+        assert rel(z, same) < tol
+    with pytest.raises(ValueError):
+        engine._regular_i8_cubic_abc(x.to(cuda_device), [(1.0, 1.0, 0.0), abc])     # b must be negative
+    with pytest.raises(ValueError):
+        CutlassNSInt8(autotune=True)._regular_i8_grouped_cubic(x.to(cuda_device), 1.0, [1.5], abc)
