@@ -137,3 +137,25 @@ def test_adamw_restatement_follows_torch_adamw():
         p = o.adamw_update(p, gr.numpy(), m, v, step, **kw)
     np.testing.assert_allclose(p, ref.detach().numpy(), rtol=2e-6, atol=2e-8)
     np.testing.assert_allclose(m, opt.state[ref]["exp_avg"].numpy(), rtol=2e-6, atol=1e-10)
+
+
+def test_factored_rows_and_grouped_cubics_restate_their_polynomials():
+    """c((G + pI)^2 + qI) is the quintic (c(p^2 + q), 2cp, c): the two INT8 restatements agree to
+    quantisation noise, and grouped cubics followed by a quintic track the same maps in FP32."""
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn((1, 48, 80), generator=g)
+    rows = [(c, b / (2 * c), a / c - (b / (2 * c)) ** 2) for a, b, c in C5[:2]]
+    factored = o.ns_int8(x, rows, fp16_first=False, factored=True)
+    plain = o.ns_int8(x, C5[:2], fp16_first=False)
+    assert float((factored - plain).norm() / plain.norm()) < 2e-2
+    first16 = o.ns_int8(x, rows, fp16_first=True, factored=True)
+    assert float((first16 - plain).norm() / plain.norm()) < 5e-2
+    abc = (3.4445, -4.775, 2.0315)
+    cubic = o.ns_int8_grouped_cubic(x, 1.0, [1.5, 1.5], abc)
+    t = x[0] / x[0].norm()
+    eye = torch.eye(48)
+    for gain in (1.5, 1.5):
+        t = -gain * ((t @ t.mT) - eye) @ t
+    gram = t @ t.mT
+    t = (abc[0] * eye + abc[1] * gram + abc[2] * gram @ gram) @ t
+    assert float((cubic[0] - t).norm() / t.norm()) < 3e-2
