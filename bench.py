@@ -214,6 +214,41 @@ def dominant_kernel_roofline(dev, peaks, source, b=4):
             "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({source}); INT8 dense rate is twice BF16"}
 
 
+def fp16_first_iteration_gemm(dev, peaks, source, b=2):
+    """Time the FP16 update GEMM of the first iteration alone (gate/up shape, transposed BF16 result)."""
+    from i8muon_b200 import native
+    from i8muon_b200.engine import status_word
+    lp, hp = 4096, 14336
+    gen = torch.Generator(device=dev).manual_seed(6)
+    q = (torch.randn((b, lp, lp), device=dev, generator=gen) * 0.05).half()
+    at = (torch.randn((b, hp, lp), device=dev, generator=gen) * 0.05).half()
+    out = torch.empty((b, hp, lp), device=dev, dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch():
+        native.call("i8m_float_gemm", q.data_ptr(), None, at.data_ptr(), None, out.data_ptr(), None, None, None,
+                    native.F16, 0, b, lp, hp, lp, lp, hp, 0, 1, 1, native.BF16, 0.0, 0.0, 0.0,
+                    status_word(dev).data_ptr(), stream)
+    for _ in range(3):
+        launch()
+    n = 10
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(n):
+        launch()
+    end.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(end) / 1e3 / n
+    flops = 2.0 * lp * lp * hp * b
+    achieved = flops / seconds / 1e12
+    peak = peaks["bf16_tflops_sustained"]
+    return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "kernel": f"wholek_persistent_kernel<EpiFloat<half, final>> B={b} 4096x14336 (k=4096), transposed bf16 result",
+            "flops_per_launch": flops, "ms_per_launch": seconds * 1e3,
+            "peak_source": f"bf16_tflops_sustained of MEASURED_PEAKS.json ({source})"}
+
+
 def run_native(args):
     import torch.distributed as dist
     from i8muon_b200 import CutlassNSInt8, check_status, native, recommend_coefficients
@@ -325,9 +360,16 @@ def main():
     parser.add_argument("--layers", type=int, default=32, help="layers of the parameter set (32 = the full set)")
     parser.add_argument("--group-bytes", type=int, default=2 << 30)
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--only-fp16", type=int, default=0, metavar="B",
+                        help="only time the FP16 first-iteration update GEMM on B matrices (small case for ncu)")
     parser.add_argument("--only-roofline", type=int, default=0, metavar="B",
                         help="only time the dominant GEMM on B matrices of 4096x14336 (small case for ncu)")
     args = parser.parse_args()
+    if args.only_fp16:
+        torch.cuda.set_device(0)
+        peaks, source = measured_peaks()
+        print(json.dumps(fp16_first_iteration_gemm(torch.device("cuda", 0), peaks, source, args.only_fp16)))
+        return
     if args.only_roofline:
         torch.cuda.set_device(0)
         peaks, source = measured_peaks()

@@ -93,8 +93,18 @@ __device__ __forceinline__ void decode_tile(const GemmGeom& g, int linear, int& 
     tm = i;
     tn = t - i * (i + 1) / 2;
   } else {
-    tm = t / g.tiles_n;
-    tn = t - tm * g.tiles_n;
+    // Row blocks are taken in groups of TILE_GROUP and walked column-major inside a group, so
+    // that the tiles in flight at one time (one or two per SM, consecutive indices) share few
+    // row blocks of both operands: with row-major order the 296 tiles of a wave spanned every
+    // column block and the right operand was re-read from DRAM once per 2.6 row blocks
+    // (1.4 GB read for 0.27 GB of operands on the 4096 x 14336 FP16 update).
+    constexpr int TILE_GROUP = 8;
+    const int per_group = TILE_GROUP * g.tiles_n;
+    const int grp = t / per_group;
+    const int in_group = t - grp * per_group;
+    const int rows = min(TILE_GROUP, g.tiles_m - grp * TILE_GROUP);
+    tn = in_group / rows;
+    tm = grp * TILE_GROUP + (in_group - tn * rows);
   }
 }
 
