@@ -207,8 +207,8 @@ def dominant_kernel_roofline(dev, peaks, source, b=4):
     achieved = flops / seconds / 1e12
     peak = 2.0 * peaks["bf16_tflops_sustained"]
     return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-            "traffic": 410.0e6 * b, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one B=1 "
-            "launch (303.5 + 106.5 MB), scaled by the batch: every batch matrix is an independent set of tiles",
+            "traffic": 386.0e6 * b, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one B=1 "
+            "launch (291.2 + 94.7 MB), scaled by the batch: every batch matrix is an independent set of tiles",
             "kernel": f"bq_persistent_kernel<EpiBq<int8, update>> B={b} 4096x14336 (k=4096)",
             "flops_per_launch": flops, "ms_per_launch": seconds * 1e3,
             "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({source}); INT8 dense rate is twice BF16"}
