@@ -13,9 +13,10 @@
 // Measured facts behind the structure (B200, update GEMM 4096 x 14336, K = 4096):
 //   * every K block has its own accumulator, so K blocks are independent work items for
 //     the tensor core; two producers and two issuers work on alternate K blocks;
-//   * a 128-byte K block of a 128x128 tile moves 32 KB into shared memory and the four
-//     MMAs read 32 KB back: 512 cycles of shared-memory time against 256 cycles of tensor
-//     time, which is where the K loop sits (about 550 cycles per K block);
+//   * a 128-byte K block of a 128x128 tile is 256 cycles of tensor work; the K loop sits at
+//     about 550 cycles per K block: the epilogue drains and refills a 64 KB accumulator every
+//     K block (the MMA itself slows to ~390 cycles per K block while eight warps read TMEM),
+//     and 32 KB go into and out of shared memory;
 //   * the epilogue loop is written for instruction count (see the step lambda): with the
 //     first, straightforward loop the kernel spent 800 cycles per K block, two to three
 //     bookkeeping instructions per useful one;
