@@ -171,6 +171,65 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------------------------------------- reference kernels on this GPU
+def run_reference_gpu(args):
+    """The reference's own optimizer and CUDA kernels (oracle/_ref, built for sm_100a) on the same set.
+
+    A same-box baseline next to the headline, not the ``--impl reference`` arm (which stays the host-core
+    path): ``Muon(...).step()`` of the unmodified reference, one Newton-Schulz call per matrix as it does,
+    its cp.async + mma.sync tiles, timed with CUDA events.
+    """
+    from oracle import reference_gpu
+    if not reference_gpu.available():
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "oracle/_ref is not built on this machine"}))
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    ref = reference_gpu.load()
+    shape_list = shapes(args.layers)
+    gen = torch.Generator(device=dev).manual_seed(4000)
+    params = [torch.nn.Parameter((torch.randn(s, device=dev, generator=gen) * 0.02).bfloat16()) for s in shape_list]
+    for p in params:
+        p.grad = (torch.randn(p.shape, device=dev, generator=gen) * 1e-3).bfloat16()
+    opt = ref.Muon(params, lr=LR, weight_decay=WD, momentum=MOMENTUM, ns_steps=NS_STEPS,
+                   adjust_lr_fn="match_rms_adamw", precision=args.precision, fp16_first=bool(args.fp16_first),
+                   use_gram=False)
+    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 2))
+    for _ in range(warmup):
+        opt.step()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        opt.step()
+    end.record()
+    torch.cuda.synchronize()
+    seconds = start.elapsed_time(end) / 1e3 / steps
+    flops = ns_flops_of(shape_list)
+    finite = all(bool(torch.isfinite(p).all()) for p in params[:7])
+    print(json.dumps({"impl": "reference-gpu", "metric": "muon_step_ns_tflops", "value": flops / seconds / 1e12,
+                      "unit": "TFLOP/s", "ms_per_step": seconds * 1e3, "steps": steps, "warmup": warmup,
+                      "config": config_dict(1, args.layers, args.precision, bool(args.fp16_first)),
+                      "finite": finite, "gpu": torch.cuda.get_device_name(0),
+                      "what": "i8muon 0.2.0 Muon.step(), its csrc/*.cu built for sm_100a (cp.async + mma.sync "
+                              "tiles), one NS call per matrix"}), flush=True)
+
+
+def reference_gpu_leg(args):
+    """Run the leg above in a child process (its 42 GB of tensors are freed with it)."""
+    from oracle import reference_gpu
+    if not reference_gpu.available():
+        return None
+    command = [sys.executable, str(ROOT / "bench.py"), "--impl", "reference-gpu", "--steps", "2", "--warmup", "1",
+               "--layers", str(args.layers), "--precision", args.precision, "--fp16-first", str(args.fp16_first)]
+    try:
+        done = subprocess.run(command, capture_output=True, text=True, timeout=600)
+        lines = [ln for ln in done.stdout.splitlines() if ln.startswith("{")]
+        return json.loads(lines[-1]) if lines else {"unavailable": (done.stderr or "no output")[-300:]}
+    except (subprocess.TimeoutExpired, json.JSONDecodeError) as err:
+        return {"unavailable": str(err)[-300:]}
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def dominant_kernel_roofline(dev, peaks, source, b=4):
     """Time the INT8 block-quantised update GEMM alone on the gate/up shape."""
@@ -354,7 +413,7 @@ def main():
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=3)
     parser.add_argument("--warmup", type=int, default=3)
-    parser.add_argument("--impl", choices=("native", "reference"), default="native")
+    parser.add_argument("--impl", choices=("native", "reference", "reference-gpu"), default="native")
     parser.add_argument("--precision", default="int8_bq")
     parser.add_argument("--fp16-first", type=int, default=1)
     parser.add_argument("--layers", type=int, default=32, help="layers of the parameter set (32 = the full set)")
@@ -377,6 +436,8 @@ def main():
         return
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     else:
         run_native(args)
 
