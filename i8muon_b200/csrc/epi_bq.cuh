@@ -4,11 +4,13 @@
 // Every 128-deep K block is accumulated on its own in tensor memory and then
 // promoted:  total = fmaf(float(partial), sA[tm,kb] * sB[.,kb], total)  in ascending
 // kb order, as in the reference (src/i8muon/csrc/bq.cu:190-195).  The tile tail
-// restates bq.cu:204-299 with un-fused FP32 operations:
+// restates bq.cu:204-299 with the fused multiply-adds that the reference's --fmad=true build
+// contains (established bit for bit, every stage, against tensors recorded from the reference's
+// own build for sm_100a: tests/golden/reference_ns_bq_*.npz); every rounding is explicit here:
 //   BQ_GRAM    diagonal -> dout (zero beyond the logical size), diagonal entry zeroed
-//   BQ_POLY    v = g_ij * sG[tm,tn];  val = (total + (d_i + d_j) * v) * cc + v * cb;
-//              diagonal: dout_i = val + (ca + d_i * (cb + d_i * cc)), entry zeroed
-//   BQ_UPDATE  val = total + (a_ij * dP_i) * sA[tm,tn]
+//   BQ_POLY    v = g_ij * sG[tm,tn];  val = fma(v, cb, fma(d_i + d_j, v, total) * cc);
+//              diagonal: dout_i = val + fma(d_i, fma(d_i, cc, cb), ca), entry zeroed
+//   BQ_UPDATE  val = fma(a_ij * dP_i, sA[tm,tn], total)
 // then (non-final) tile max (floor 1e-8) -> scale, quantise (INT8 truncates toward
 // zero, E4M3 rounds to nearest even and saturates), store the tile and its
 // mirror / transpose; the final update casts to the user's dtype instead.
@@ -240,17 +242,15 @@ struct EpiBq {
           if constexpr (MODE == BQ_POLY) {
             const float v = __fmul_rn(bq_decode<FP8>(q), stile);
             const float dcol = t.diag[c0 + j];
-            val = __fadd_rn(val, __fmul_rn(__fadd_rn(drow, dcol), v));
-            val = __fmul_rn(val, a.cc);
-            val = __fadd_rn(val, __fmul_rn(v, a.cb));
+            val = __fmaf_rn(__fadd_rn(drow, dcol), v, val);
+            val = __fmaf_rn(v, a.cb, __fmul_rn(val, a.cc));
             if (has_diag && col == t.row) {
-              const float dpoly =
-                  __fadd_rn(a.ca, __fmul_rn(drow, __fadd_rn(a.cb, __fmul_rn(drow, a.cc))));
+              const float dpoly = __fmaf_rn(drow, __fmaf_rn(drow, a.cc, a.cb), a.ca);
               if (live) a.dout[size_t(t.b) * g.m + t.row] = in_rows ? __fadd_rn(val, dpoly) : 0.f;
               val = 0.f;
             }
           } else {
-            val = __fadd_rn(val, __fmul_rn(__fmul_rn(bq_decode<FP8>(q), drow), stile));
+            val = __fmaf_rn(__fmul_rn(bq_decode<FP8>(q), drow), stile, val);
           }
         }
         if (!inside && (!in_rows || col >= g.ln)) val = 0.f;  // padding never contributes to a block scale
@@ -296,14 +296,21 @@ struct EpiBq {
       return;
     } else {
       mx = warp_max(mx);
-      if (t.lane == 0) t.red[t.ew] = mx;
+      // A warp whose wait ran out publishes a negative value (a maximum is >= 1e-8), so that all
+      // eight warps take the same decision: either every warp stores this tile or none does, and
+      // every warp walks through the same barriers below whatever it decided.
+      if (t.lane == 0) t.red[t.ew] = live ? mx : -1.f;
       named_bar_sync(1, EPI_THREADS);
-      if (!live) return;
+      bool store = true;
 #pragma unroll
-      for (int i = 0; i < EPI_WARPS; ++i) mx = fmaxf(mx, t.red[i]);
+      for (int i = 0; i < EPI_WARPS; ++i) {
+        const float other = t.red[i];
+        store = store && other >= 0.f;
+        mx = fmaxf(mx, other);
+      }
       const float multiplier = QMAX / mx;
       const float scale = 1.f / multiplier;
-      if (t.r == 0 && t.half == 0) {
+      if (store && t.r == 0 && t.half == 0) {
         a.so[(size_t(t.b) * mq + t.tm) * nq + t.tn] = scale;
         if constexpr (MODE != BQ_UPDATE) a.so[(size_t(t.b) * mq + t.tn) * nq + t.tm] = scale;
       }
@@ -323,6 +330,7 @@ struct EpiBq {
       const bool staged_t = tsm != nullptr;
       const uint32_t tsm_s = tsm ? smem_u32(tsm) + uint32_t(c0 * TSM_PITCH + t.r) : 0u;      // (column, row)
       const uint32_t tsm_own = tsm ? smem_u32(tsm) + uint32_t(t.r * TSM_PITCH + c0) : 0u;    // (row, column)
+      if (store)
 #pragma unroll
       for (int c16 = 0; c16 < CPT / 16; ++c16) {
         uint32_t w[4];
@@ -358,6 +366,7 @@ struct EpiBq {
         // 128 staged rows of 128 bytes = 1024 chunks of 16 bytes over 256 threads; a staged row
         // is a column of this tile, i.e. a row of the transposed / mirrored tile
         const int tid = t.ew * 32 + t.lane;
+        if (store)
 #pragma unroll
         for (int i = 0; i < (TILE * TILE / 16) / EPI_THREADS; ++i) {
           const int chunk = tid + i * EPI_THREADS;

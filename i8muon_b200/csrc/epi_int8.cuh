@@ -1,15 +1,19 @@
 // Fused epilogues of the global-scale INT8 Newton-Schulz GEMMs (tcgen05 kind::i8,
 // int32 accumulation in tensor memory).
 //
-// Arithmetic restates the reference's INT8 GEMM modes (src/i8muon/csrc/int8.cu:254-352)
-// with every FP32 operation written un-fused so that a CPU restatement can
-// reproduce it bit for bit:
+// Arithmetic restates the reference's INT8 GEMM modes (src/i8muon/csrc/int8.cu:254-352).
+// The reference is compiled with --fmad=true, so its unannotated expressions contain fused
+// multiply-adds; which ones was established against tensors recorded from the reference's own
+// build for sm_100a (tests/golden/reference_ns_i8_*.npz).  This library is compiled with
+// --fmad=false and writes every rounding explicitly, so that a CPU restatement reproduces it:
 //   I8_GRAM    G32 = A8 * A8^T  (lower tiles), gmax = max_{i != j} |G32_ij|   (int32, exact)
-//   I8_SQUARE  P_ij = g8_ij * (r_i + c_j) + (g8*g8)_ij * (gs*gs*c)
-//              r_i = (dG_i*c + b)*gs, c_j = (dG_j*gs)*c ;
+//   I8_SQUARE  P_ij = fma((g8*g8)_ij, gs*gs*c, g8_ij * t_ij),
+//              t_ij = fma(fma(dG_i, c, b), gs, (dG_j*gs)*c)
+//              (the reference's binary uses this form for about three quarters of the elements and
+//              fma(dG_j*gs, c, (fma(dG_i,c,b))*gs) for the rest, by unrolled instance: 1 ulp apart);
 //              pmax = max |P_ij| over i != j, floor(i/128) >= floor(j/128)
-//   I8_UPDATE  Y_ij = (a8_ij * dP_i + (p8*a8)_ij * ps) * as ; non-final keeps FP32 + max,
-//              final casts to the user's dtype, un-pads, optionally transposes.
+//   I8_UPDATE  Y_ij = fma(a8_ij, dP_i, (p8*a8)_ij * ps) * as  (the reference's binary, every element);
+//              non-final keeps FP32 + max, final casts to the user's dtype, un-pads, optionally transposes.
 #pragma once
 #include "epi_float.cuh"
 
@@ -50,14 +54,14 @@ struct EpiI8 {
     const bool row_ok = t.row < g.m;
     int imax = 0;
     float fmax_ = 0.f;
-    float sa = 0.f, sb = 0.f, sq = 0.f, drow = 0.f, ri = 0.f;
+    float sa = 0.f, sb = 0.f, sq = 0.f, drow = 0.f, xrow = 0.f;
     if constexpr (MODE != I8_GRAM) {
       sa = a.a_scale[t.b];
       if (row_ok) drow = a.diag[size_t(t.b) * g.m + t.row];
     }
     if constexpr (MODE == I8_SQUARE) {
       sq = __fmul_rn(__fmul_rn(sa, sa), a.beta);
-      ri = __fmul_rn(__fadd_rn(__fmul_rn(drow, a.beta), a.alpha), sa);
+      xrow = __fmaf_rn(drow, a.beta, a.alpha);
     }
     if constexpr (MODE == I8_UPDATE || MODE == I8_UPDATE_FINAL) {
       sb = a.b_scale[t.b];
@@ -95,11 +99,11 @@ struct EpiI8 {
           if constexpr (MODE == I8_SQUARE) {
             float dcol = (col < g.n) ? a.diag[size_t(t.b) * g.m + col] : 0.f;
             float cj = __fmul_rn(__fmul_rn(dcol, sa), a.beta);
-            r = __fadd_rn(__fmul_rn(e, __fadd_rn(ri, cj)), __fmul_rn(accf, sq));
+            r = __fmaf_rn(accf, sq, __fmul_rn(e, __fmaf_rn(xrow, sa, cj)));
             if (col != t.row && (t.row >> 7) >= (col >> 7) && t.row < g.lm && col < g.ln)
               fmax_ = fmaxf(fmax_, fabsf(r));
           } else {
-            r = __fmul_rn(__fadd_rn(__fmul_rn(e, drow), __fmul_rn(accf, sa)), sb);
+            r = __fmul_rn(__fmaf_rn(e, drow, __fmul_rn(accf, sa)), sb);
             if (MODE == I8_UPDATE && t.row < g.lm && col < g.ln) fmax_ = fmaxf(fmax_, fabsf(r));
           }
           res[j] = r;

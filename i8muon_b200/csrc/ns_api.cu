@@ -23,9 +23,13 @@ using namespace i8m;
 namespace {
 
 thread_local char g_error[512] = "";
-int g_debug_simt = 0;
-int g_wholek_persistent = 1;   // 0: one CTA per tile (variant 1 of "wholek_gemm")
-int g_bq_variant = 0;   // 0: six-stage ring, 1: four-stage ring (chosen by the host-side tuner)
+// Kernel selection is per calling thread: two engines on two threads (or two devices driven
+// from two threads) never see each other's choice.  i8m_ns_run additionally takes the
+// selection as an argument and restores the thread's own setting when it returns.
+thread_local int g_debug_simt = 0;
+thread_local int g_wholek_persistent = 1;   // 0: one CTA per tile (variant 1 of "wholek_gemm")
+thread_local int g_bq_variant = 0;   // 0: six-stage ring, 1: four-stage ring (chosen by the host-side tuner)
+constexpr int BQ_VARIANTS = 2;
 std::atomic<unsigned long long> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
@@ -270,14 +274,16 @@ extern "C" int i8m_set_variant(const char* operation, int variant) {
 // ================================================================== stats
 extern "C" int i8m_stats_scratch_bytes(int batch, long long count, size_t* bytes) {
   if (batch < 1 || count < 1 || !bytes) return fail(I8M_E_ARGUMENT, "stats_scratch_bytes: bad argument");
-  *bytes = size_t(2) * batch * cdiv(count, STATS_CHUNK) * sizeof(float);
+  if (count / STATS_CHUNK >= 0x7fffffffLL) return fail(I8M_E_LIMIT, "stats_scratch_bytes: count %lld is too large", count);
+  *bytes = size_t(2) * batch * size_t(count / STATS_CHUNK + (count % STATS_CHUNK != 0)) * sizeof(float);
   return 0;
 }
 extern "C" int i8m_stats(const void* x, int dtype, int batch, long long count, void* scratch,
                          size_t scratch_bytes, float* norm, float* amax, i8m_stream_t stream) {
   if (!x || !scratch || batch < 1 || batch > 65535 || count < 1 || !float_dtype_ok(dtype))
     return fail(I8M_E_ARGUMENT, "stats: bad argument");
-  const int chunks = cdiv(count, STATS_CHUNK);
+  if (count / STATS_CHUNK >= 0x7fffffffLL) return fail(I8M_E_LIMIT, "stats: count %lld is too large", count);
+  const int chunks = int(count / STATS_CHUNK + (count % STATS_CHUNK != 0));
   size_t need = size_t(2) * batch * chunks * sizeof(float);
   if (scratch_bytes < need) return fail(I8M_E_WORKSPACE, "stats: scratch %zu < %zu bytes", scratch_bytes, need);
   float* psum = static_cast<float*>(scratch);
@@ -305,9 +311,9 @@ extern "C" int i8m_stats_static(const void* x, int dtype, int batch, long long c
                                 float* amax, i8m_stream_t stream) {
   if (!x || batch < 1 || batch > 65535 || count < 1 || !float_dtype_ok(dtype))
     return fail(I8M_E_ARGUMENT, "stats_static: bad argument");
-  const long long chunks = (count + STATS_CHUNK - 1) / STATS_CHUNK;
-  const unsigned long long need = 2ull * (unsigned long long)batch * (unsigned long long)chunks;
-  if (need > STATIC_SCRATCH_FLOATS)
+  // no sum or product here can wrap: chunks is compared with the limit before it is multiplied
+  const long long chunks = count / STATS_CHUNK + (count % STATS_CHUNK != 0);
+  if (chunks > (long long)(STATIC_SCRATCH_FLOATS / 2) / batch)
     return fail(I8M_E_LIMIT,
                 "stats_static: batch * ceil(count / 8192) = %lld exceeds the built-in scratch of %zu "
                 "partials; use i8m_stats with caller scratch",
@@ -967,7 +973,7 @@ extern "C" int i8m_ns_workspace_bytes(int route, int batch, int rows, int cols, 
 
 extern "C" int i8m_ns_run(int route, const void* x, void* out, int dtype, int batch, int rows,
                           int cols, int compute, const double* coeffs, int steps, float eps,
-                          int fp16_first, const char* gram_order, void* workspace,
+                          int fp16_first, int variants, const char* gram_order, void* workspace,
                           size_t workspace_bytes, uint32_t* status, i8m_stream_t stream) {
   if (!x || !out || !coeffs || !workspace || !status) return fail(I8M_E_ARGUMENT, "ns_run: null pointer");
   if (x == out) return fail(I8M_E_ARGUMENT, "ns_run: out may not alias x");
@@ -983,5 +989,15 @@ extern "C" int i8m_ns_run(int route, const void* x, void* out, int dtype, int ba
   c.x = x; c.out = out; c.coeffs = coeffs; c.eps = eps; c.gram_order = gram_order;
   c.status = status; c.stream = S(stream);
   Bump ws(workspace, workspace_bytes, false);
-  return ns_dispatch(c, ws, false);
+  if (variants < 0) return ns_dispatch(c, ws, false);
+  // this call's own kernel selection; the thread's setting comes back whatever happens
+  const int bq = variants & 0xff, wholek = (variants >> 8) & 0xff;
+  if (bq >= BQ_VARIANTS || wholek >= 2) return fail(I8M_E_ARGUMENT, "ns_run: unknown kernel variant 0x%x", variants);
+  const int saved_bq = g_bq_variant, saved_wholek = g_wholek_persistent;
+  g_bq_variant = bq;
+  g_wholek_persistent = wholek == 0 ? 1 : 0;
+  const int rc = ns_dispatch(c, ws, false);
+  g_bq_variant = saved_bq;
+  g_wholek_persistent = saved_wholek;
+  return rc;
 }

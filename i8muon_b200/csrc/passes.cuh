@@ -350,11 +350,11 @@ symmetric_quant_kernel(const In* input, const void* maximum, const float* orig_s
     if (row == col && row < m) {
       if constexpr (QUAD) {
         const float d = orig_diag[size_t(b) * m + row];
-        diag[size_t(b) * m + row] =
-            __fadd_rn(__fadd_rn(v, __fmul_rn(__fadd_rn(__fmul_rn(c2, d), c1), d)), c0);
+        // the reference's binary (--fmad=true) fuses both products of v + (c2*d + c1)*d + c0
+        diag[size_t(b) * m + row] = __fadd_rn(__fmaf_rn(__fmaf_rn(c2, d, c1), d, v), c0);
       } else {
         // c0 shifts the Gram diagonal (completed-square rows, int8.cu:396); it is 0 otherwise
-        diag[size_t(b) * m + row] = __fadd_rn(__fmul_rn(v, sa), c0);
+        diag[size_t(b) * m + row] = __fmaf_rn(v, sa, c0);
       }
     }
     tile[r][tx] = q;

@@ -57,6 +57,37 @@ def check_status(device=None) -> None:
             raise native.NativeError(f"device-side wait timed out, status word 0x{code:x}")
 
 
+_STATUS_HOST = {}
+
+
+def post_status(device) -> None:
+    """Queue a copy of the device's status word to pinned host memory on the current stream; nothing
+    waits for it.  ``raise_if_reported`` looks at the copy once it has landed."""
+    index = torch.device(device).index
+    index = torch.cuda.current_device() if index is None else index
+    word = _STATUS_WORDS.get(index)
+    if word is None or torch.cuda.is_current_stream_capturing():
+        return
+    slot = _STATUS_HOST.get(index)
+    if slot is None:
+        slot = _STATUS_HOST[index] = (torch.zeros(1, dtype=torch.int32).pin_memory(), torch.cuda.Event())
+    host, event = slot
+    with torch.cuda.device(index):
+        host.copy_(word, non_blocking=True)
+        event.record()
+
+
+def raise_if_reported() -> None:
+    """Raise if a status word copied by ``post_status`` has arrived and is not zero (no synchronisation)."""
+    for index, (host, event) in _STATUS_HOST.items():
+        if event.query() and int(host[0]) != 0:
+            code = int(host[0])
+            host.zero_()
+            _STATUS_WORDS[index].zero_()
+            raise native.NativeError(f"device-side wait timed out on cuda:{index}, status word 0x{code:x}; the "
+                                     "results of the previous step are incomplete")
+
+
 def _coefficient_array(coeffs):
     rows = [tuple(float(v) for v in row) for row in coeffs]
     if not rows or any(len(row) != 3 for row in rows):
@@ -107,10 +138,9 @@ class CutlassNSInt8:
                 raise ValueError("out must be a contiguous tensor like x that does not alias it")
 
             def launch(variant):
-                native.call("i8m_set_variant", b"bq_gemm", int(variant))
                 workspace = torch.empty(size, dtype=torch.uint8, device=x.device)
                 native.call("i8m_ns_run", route, x.data_ptr(), out.data_ptr(), dtype, batch, rows, cols,
-                            compute, array, steps, float(eps), int(bool(fp16_first)),
+                            compute, array, steps, float(eps), int(bool(fp16_first)), int(variant),
                             order.encode() if order is not None else None, workspace.data_ptr(), size,
                             status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
 
@@ -178,4 +208,4 @@ class CutlassNSInt8:
         return self._run(native.ROUTE_BQ_FP8, x, coeffs, eps, native.F16, 128, precision, False, out)
 
 
-__all__ = ["CutlassNSInt8", "check_status", "status_word"]
+__all__ = ["CutlassNSInt8", "check_status", "status_word", "post_status", "raise_if_reported"]

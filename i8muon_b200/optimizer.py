@@ -10,12 +10,14 @@ the device:
     stacked update tensor directly, and weight decay + the learning-rate-scaled
     update is one multi-tensor kernel; their roundings match the eager torch
     sequence of the reference;
-  * with ``use_cuda_graph`` the momentum kernel and the whole Newton-Schulz call
-    of a group are captured together and replayed; the apply kernel stays
-    outside the graph so that learning-rate schedules keep working.
+  * with ``use_cuda_graph`` the whole Newton-Schulz call of a group (some thirty launches) is
+    captured over a static update buffer and replayed; the two multi-tensor kernels run eagerly
+    around it because they take the addresses of gradients and parameters and the learning
+    rate as arguments, so the graph survives re-allocated gradients and learning-rate schedules.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 from typing import Optional
 
@@ -25,7 +27,7 @@ from torch.optim.optimizer import Optimizer, ParamsT
 
 from . import native
 from .coefficients import recommend_coefficients
-from .engine import CutlassNSInt8
+from .engine import CutlassNSInt8, post_status, raise_if_reported
 from .routing import (EPS, GRAM_ASPECT_THRESHOLD, adjust_lr, matrix_spec, normalize_precision,
                       validate_ns_device)
 
@@ -36,39 +38,53 @@ __all__ = ["Muon", "muon_step", "native_step_ops"]
 MAX_GROUP_BYTES = int(os.environ.get("I8MUON_B200_MAX_GROUP_BYTES", str(2 << 30)))
 
 
-def _check_group(group) -> None:
-    lr = group["lr"]
-    if isinstance(lr, Tensor) and lr.numel() != 1:
-        raise ValueError("Tensor lr must be 1-element")
-    for name in ("weight_decay", "eps"):
-        if not 0.0 <= group[name]:
-            raise ValueError(f"{name} must be >= 0")
-    coeffs = group["ns_coefficients"]
-    if coeffs is not None and (not coeffs or any(len(row) != 3 for row in coeffs)):
-        raise ValueError("Expected a nonempty list of (a, b, c) coefficients")
-    momentum = group["momentum"]
-    if isinstance(momentum, (int, float)):
-        momentum = (momentum,)
-    if len(momentum) not in (1, 2) or any(not 0.0 <= m for m in momentum):
+# ------------------------------------------------------------------ group settings
+# One rule per setting: (name, test on the value, message).  The messages are part of the
+# drop-in contract (src/i8muon/_optimizer.py:39-67); the table is this library's own.
+_ADJUST_NAMES = ("spectral", "original", "match_rms_adamw", "none")
+_DECAY_MODES = ("absolute", "base_lr", "adjusted_lr")
+
+
+def _momentum_tuple(value):
+    values = (value,) if isinstance(value, (int, float)) else tuple(value)
+    if len(values) not in (1, 2) or any(not 0.0 <= m for m in values):
         raise ValueError("momentum must contain one or two nonnegative values")
-    group["momentum"] = tuple(momentum)
-    adjust = group["adjust_lr_fn"]
-    if adjust is not None and not callable(adjust) and adjust not in (
-            "spectral", "original", "match_rms_adamw", "none"):
-        raise ValueError(f"adjust_lr_fn {adjust} is not supported")
+    return values
+
+
+_GROUP_RULES = (
+    ("lr", lambda v: not isinstance(v, Tensor) or v.numel() == 1, "Tensor lr must be 1-element"),
+    ("weight_decay", lambda v: 0.0 <= v, "weight_decay must be >= 0"),
+    ("eps", lambda v: 0.0 <= v, "eps must be >= 0"),
+    ("ns_coefficients", lambda v: v is None or (len(v) > 0 and all(len(row) == 3 for row in v)),
+     "Expected a nonempty list of (a, b, c) coefficients"),
+    ("adjust_lr_fn", lambda v: v is None or callable(v) or v in _ADJUST_NAMES, None),
+    ("weight_decay_mode", lambda v: v in _DECAY_MODES,
+     "weight_decay_mode must be 'absolute', 'base_lr' or 'adjusted_lr'"),
+)
+
+
+def _check_group(group) -> None:
+    """Validate one parameter group's settings and bring momentum / precision to canonical form."""
+    for name, accept, message in _GROUP_RULES:
+        if not accept(group[name]):
+            raise ValueError(message or f"{name} {group[name]} is not supported")
+    group["momentum"] = _momentum_tuple(group["momentum"])
     group["precision"] = normalize_precision(group["precision"])
-    if group["weight_decay_mode"] not in ("absolute", "base_lr", "adjusted_lr"):
-        raise ValueError("weight_decay_mode must be 'absolute', 'base_lr' or 'adjusted_lr'")
 
 
-def _graph_key(ns_fn, layout, count, precision, coefficients, eps, deterministic, engine, momentum,
-               pointers):
-    """One graph owns the addresses and constants of one group's momentum + NS."""
+def _graph_key(ns_fn, layout, count, precision, coefficients, eps, deterministic, engine):
+    """What one captured Newton-Schulz call depends on.  No tensor address is part of it: the graph
+    reads a static update buffer and writes a static result, so it outlives re-allocated gradients
+    (``zero_grad(set_to_none=True)``), as the reference's does (src/i8muon/_optimizer.py:133-139, 476-497)."""
     schedule = recommend_coefficients() if coefficients is None else coefficients
-    return (engine, ns_fn.__name__, layout.device, layout.dtype, tuple(layout.shape), count, precision,
+    return (id(engine), ns_fn.__name__, layout.device, layout.dtype, tuple(layout.shape), count, precision,
             tuple(tuple(row) for row in schedule), eps, deterministic, engine.fp16_first,
-            tuple(sorted(engine.tiles.items())), os.environ.get("I8MUON_GRAM_RESET", "00100"),
-            momentum, pointers)
+            tuple(sorted(engine.tiles.items())), os.environ.get("I8MUON_GRAM_RESET", "00100"))
+
+
+# captured graphs kept per optimizer; the least recently used one is dropped beyond this
+MAX_CAPTURED_GRAPHS = int(os.environ.get("I8MUON_B200_MAX_GRAPHS", "64"))
 
 
 class Muon(Optimizer):
@@ -88,6 +104,11 @@ class Muon(Optimizer):
     schedule.  ``adjust_lr_fn``: "spectral", "original", "match_rms_adamw",
     "none"/None, or a callable (lr, rows, cols).  ``weight_decay_mode``:
     "base_lr" (default), "adjusted_lr" or "absolute".
+
+    A device-side wait that runs out (it never should) is reported through a status word.
+    ``step()`` reads it without stalling: the word is copied to pinned host memory at the end of
+    a step and examined at the start of the next one, which then raises ``NativeError``;
+    ``check_status()`` synchronises and examines it at once.
     """
 
     def __init__(
@@ -124,18 +145,17 @@ class Muon(Optimizer):
                         adjust_lr_fn=adjust_lr_fn, deterministic=deterministic, use_gram=use_gram,
                         precision=precision)
         super().__init__(params, defaults)
-        self._require_disjoint(scalar_optimizer, self._all_matrix_ids())
+        self._refuse_shared_parameters(scalar_optimizer, self._muon_param_groups)
         self.scalar_optimizer = scalar_optimizer
 
     # ---------------------------------------------------------- validation
-    def _all_matrix_ids(self):
-        return {id(p) for group in self._muon_param_groups for p in group["params"]}
-
     @staticmethod
-    def _require_disjoint(scalar, matrix_ids):
+    def _refuse_shared_parameters(scalar, muon_groups):
+        """A parameter belongs to Muon or to the scalar optimizer, never to both."""
         if scalar is None:
             return
-        if any(id(p) in matrix_ids for group in scalar.param_groups for p in group["params"]):
+        theirs = {id(p) for group in scalar.param_groups for p in group["params"]}
+        if any(id(p) in theirs for group in muon_groups for p in group["params"]):
             raise ValueError("Muon and scalar_optimizer must have disjoint parameters")
 
     def _validate_param_group(self, group):
@@ -149,23 +169,25 @@ class Muon(Optimizer):
                 matrix_spec(tuple(p.shape), p.dtype, p.device, compute,
                             128 if method.__name__ == "_regular_bq" else 16)
 
-    def add_param_group(self, param_group):
-        group = dict(param_group)
-        params = group["params"]
-        if isinstance(params, Tensor):
-            params = [params]
-        if isinstance(params, set):
-            raise TypeError("Optimizer parameters must have a deterministic order")
-        group["params"] = list(params)
-        merged = dict(self.defaults, **group)
-        self._validate_param_group(merged)
-        scalar = self.scalar_optimizer
-        self._require_disjoint(scalar, {id(p) for p in group["params"]})
-        self.scalar_optimizer = None
+    @contextlib.contextmanager
+    def _muon_groups_only(self):
+        """While active, ``param_groups`` and the base class see the Muon groups alone."""
+        scalar, self.scalar_optimizer = self.scalar_optimizer, None
         try:
-            super().add_param_group(merged)
+            yield scalar
         finally:
             self.scalar_optimizer = scalar
+
+    def add_param_group(self, param_group):
+        members = param_group["params"]
+        if isinstance(members, set):
+            raise TypeError("Optimizer parameters must have a deterministic order")
+        members = [members] if isinstance(members, Tensor) else list(members)
+        settings = {**self.defaults, **param_group, "params": members}
+        self._validate_param_group(settings)
+        self._refuse_shared_parameters(self.scalar_optimizer, [settings])
+        with self._muon_groups_only():
+            super().add_param_group(settings)
 
     # -------------------------------------------- param_groups / state dict
     @property
@@ -181,38 +203,33 @@ class Muon(Optimizer):
         self._muon_param_groups = value
 
     def __setstate__(self, state):
-        state = dict(state)
-        if "param_groups" in state:
-            state["_muon_param_groups"] = state.pop("param_groups")
-        super().__setstate__(state)
+        # pickles and checkpoints carry the Muon groups under the base class's name
+        renamed = {("_muon_param_groups" if key == "param_groups" else key): value for key, value in state.items()}
+        super().__setstate__(renamed)
         for group in self._muon_param_groups:
-            # checkpoints written before weight_decay_mode existed decayed with the adjusted rate
-            group.setdefault("weight_decay_mode", "adjusted_lr")
-
-    def _without_scalar(self, fn, *args):
-        scalar, self.scalar_optimizer = self.scalar_optimizer, None
-        try:
-            return fn(*args)
-        finally:
-            self.scalar_optimizer = scalar
+            if "weight_decay_mode" not in group:
+                # written before the setting existed, when the decay used the adjusted rate
+                group["weight_decay_mode"] = "adjusted_lr"
 
     def state_dict(self):
         """Muon state only; the scalar optimizer keeps its own state dict."""
-        return self._without_scalar(super().state_dict)
+        with self._muon_groups_only():
+            return super().state_dict()
 
     def load_state_dict(self, state_dict):
-        def load():
+        with self._muon_groups_only():
             Optimizer.load_state_dict(self, state_dict)
             self._ns_graphs.clear()
-        return self._without_scalar(load)
 
     # ---------------------------------------------------------------- step
     def step(self, closure=None):
         with torch.no_grad():
+            raise_if_reported()
             loss = None
             if closure is not None:
                 with torch.enable_grad():
                     loss = closure()
+            devices = set()
             for group in self._muon_param_groups:
                 params, grads, bufs = [], [], []
                 for p in group["params"]:
@@ -226,6 +243,7 @@ class Muon(Optimizer):
                     params.append(p)
                     grads.append(p.grad)
                     bufs.append(buf)
+                    devices.add(p.device)
                 muon_step(params, grads, bufs, lr=group["lr"], weight_decay=group["weight_decay"],
                           weight_decay_mode=group["weight_decay_mode"], momentum=group["momentum"],
                           ns_coefficients=group["ns_coefficients"], eps=group["eps"],
@@ -233,6 +251,8 @@ class Muon(Optimizer):
                           ns_engine=self._ns, precision=group["precision"], use_gram=group["use_gram"],
                           use_cuda_graph=self._use_cuda_graph, ns_graphs=self._ns_graphs,
                           gram_aspect_threshold=self._gram_aspect_threshold)
+            for device in devices:
+                post_status(device)
             if self.scalar_optimizer is not None:
                 self.scalar_optimizer.step()
             return loss
@@ -242,12 +262,12 @@ def _as_float(value) -> float:
     return float(value.item()) if isinstance(value, Tensor) else float(value)
 
 
-def _momentum_and_ns(grads, bufs, update, ns_fn, ns_kwargs, w_buf, mu, nesterov):
-    stream = torch.cuda.current_stream().cuda_stream
+def _momentum(grads, bufs, update, w_buf, mu, nesterov):
+    """buf <- lerp(buf, grad, w_buf); update[i] <- lerp(grad, buf, mu) (Nesterov) or buf: one launch per 32 tensors."""
     native.call("i8m_momentum", native.pointer_array([g.data_ptr() for g in grads]),
                 native.pointer_array([b.data_ptr() for b in bufs]), len(grads), update.data_ptr(),
-                grads[0].numel(), native.torch_dtype_code(update.dtype), w_buf, mu, int(nesterov), stream)
-    return ns_fn(update, **ns_kwargs)
+                grads[0].numel(), native.torch_dtype_code(update.dtype), w_buf, mu, int(nesterov),
+                torch.cuda.current_stream().cuda_stream)
 
 
 def muon_step(
@@ -325,32 +345,34 @@ def muon_step(
                         c = p.contiguous(); copy_back.append((p, c)); p = c
                     b_list.append(b); p_list.append(p)
                 count = len(part)
-                if use_cuda_graph and not copy_back:
-                    pointers = tuple(t.data_ptr() for t in g_list + b_list)
-                    key = _graph_key(ns_fn, g_list[0], count, actual, ns_coefficients, eps, deterministic,
-                                     ns_engine, (mu, mu2, nesterov), pointers)
-                    captured = ns_graphs.get(key)
+                update = None
+                if use_cuda_graph:
+                    key = _graph_key(ns_fn, g_list[0], count, actual, ns_coefficients, eps, deterministic, ns_engine)
+                    captured = ns_graphs.pop(key, None)
                     if captured is None:
+                        # The graph holds the Newton-Schulz call only, over a static update buffer and a
+                        # static result.  The momentum kernel (which takes the gradients' addresses) and the
+                        # decay + update kernel (addresses of the parameters, the learning rate) run eagerly,
+                        # so neither re-allocated gradients nor a learning-rate schedule invalidates it.
                         update = torch.empty((count, *shape), device=device, dtype=gdtype)
-                        # Warm up outside capture on copies so the real buffers are not advanced.
-                        scratch_b = [b.clone() for b in b_list]
-                        for _ in range(2):
-                            _momentum_and_ns(g_list, scratch_b, update, ns_fn, ns_kwargs, 1.0 - mu2, mu, nesterov)
-                        del scratch_b
+                        update.zero_()
+                        for _ in range(2):   # warm up outside capture: first-use work, the tuner, workspaces
+                            ns_fn(update, **ns_kwargs)
                         torch.cuda.current_stream().synchronize()
                         graph = torch.cuda.CUDAGraph()
                         with torch.cuda.graph(graph):
-                            ortho = _momentum_and_ns(g_list, b_list, update, ns_fn, ns_kwargs,
-                                                     1.0 - mu2, mu, nesterov)
-                        # keep the tensors whose addresses the graph holds alive
-                        captured = ns_graphs[key] = (graph, update, ortho, g_list, b_list)
-                    else:
-                        pass
-                    captured[0].replay()
-                    ortho = captured[2]
+                            ortho = ns_fn(update, **ns_kwargs)
+                        captured = (graph, update, ortho)
+                    ns_graphs[key] = captured            # most recently used last
+                    while len(ns_graphs) > MAX_CAPTURED_GRAPHS:
+                        ns_graphs.pop(next(iter(ns_graphs)))
+                    graph, update, ortho = captured
+                    _momentum(g_list, b_list, update, 1.0 - mu2, mu, nesterov)
+                    graph.replay()
                 else:
                     update = torch.empty((count, *shape), device=device, dtype=gdtype)
-                    ortho = _momentum_and_ns(g_list, b_list, update, ns_fn, ns_kwargs, 1.0 - mu2, mu, nesterov)
+                    _momentum(g_list, b_list, update, 1.0 - mu2, mu, nesterov)
+                    ortho = ns_fn(update, **ns_kwargs)
 
                 if callable(adjust_lr_fn):
                     adjusted = adjust_lr(lr, adjust_lr_fn, shape)

@@ -169,6 +169,11 @@ class ShardedMuonStep:
         if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream(device=device)
         ready = []
+        if any(self._consumed.get(c) is None for c, (g, first, width, _) in enumerate(chunks)
+               if g.slots[self.rank][first:first + width]):
+            # nothing recorded yet says when these gradient tensors were last touched (a fill, an earlier
+            # use): order the copies after everything already queued on the compute stream
+            self._copy_stream.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(self._copy_stream):
             for c, (g, first, width, _) in enumerate(chunks):
                 consumed = self._consumed.get(c)
@@ -196,7 +201,9 @@ class ShardedMuonStep:
                 if ready is not None and ready[c] is not None:
                     torch.cuda.current_stream(like.device).wait_event(ready[c])
                 self.ops.momentum([grads[i] for i in mine], [buffers[i] for i in mine], send)
-                if ready is not None and like.device.type == "cuda":
+                if like.device.type == "cuda":
+                    # recorded on every step, streamed or not: a later streamed step must not overwrite
+                    # a gradient that this step's momentum kernel is still reading
                     consumed = torch.cuda.Event()
                     consumed.record(torch.cuda.current_stream(like.device))
                     self._consumed[c] = consumed

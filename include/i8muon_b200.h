@@ -67,7 +67,9 @@ int i8m_set_debug_core(int simt);
  * operation "bq_gemm": 0 = six-stage operand ring (default), 1 = four-stage ring.
  * operation "wholek_gemm" (FP16/BF16/global-INT8 products): 0 = persistent kernel, one CTA per
  * SM (default), 1 = one CTA per output tile.
- * The choice is process-wide and applies to launches made after the call. */
+ * The choice belongs to the calling thread (two engines on two threads never see each other's)
+ * and applies to the stage-level launches that thread makes afterwards; i8m_ns_run takes its own
+ * selection as an argument. */
 int i8m_variant_count(const char* operation);
 int i8m_set_variant(const char* operation, int variant);
 
@@ -163,6 +165,9 @@ int i8m_bq_gemm(int fp8, int mode, const void* a, const float* sa, const float* 
  *   compute      floating routes: I8M_F32 / I8M_F16 / I8M_BF16 (ignored otherwise)
  *   coeffs       steps rows of (a, b, c), host memory
  *   fp16_first   INT8 and BQ-INT8 routes: first row in FP16, rest quantised
+ *   variants     kernel variants for this call: -1 = the calling thread's i8m_set_variant choices,
+ *                otherwise (bq_gemm variant) | (wholek_gemm variant << 8); the thread's own
+ *                choices are untouched
  *   gram_order   GRAM route: restart string such as "00100" (NULL = default)
  *   workspace    device memory of at least i8m_ns_workspace_bytes(...) bytes,
  *                256-byte aligned; contents are scratch
@@ -171,7 +176,7 @@ int i8m_ns_workspace_bytes(int route, int batch, int rows, int cols, int dtype, 
                            int steps, int fp16_first, size_t* bytes);
 int i8m_ns_run(int route, const void* x_device, void* out_device, int dtype, int batch, int rows,
                int cols, int compute, const double* coeffs, int steps, float eps, int fp16_first,
-               const char* gram_order, void* workspace_device, size_t workspace_bytes,
+               int variants, const char* gram_order, void* workspace_device, size_t workspace_bytes,
                uint32_t* status_device, i8m_stream_t stream);
 
 /* ---- optimizer step kernels ------------------------------------------------

@@ -261,7 +261,7 @@ def test_autotuned_engine_and_kernel_variants_give_identical_results(cuda_device
     assert native.library().i8m_variant_count(b"bq_gemm") == 2
     try:
         native.call("i8m_set_variant", b"bq_gemm", 1)
-        # the engine sets the variant itself on every call, so drive the stage directly
+        # the engine passes its own selection with every call, so drive the stage directly
         a, at, sa = H.bq_quant(x, None, False)
         native.call("i8m_set_variant", b"bq_gemm", 0)
         g0 = H.bq_gemm(False, 0, a, sa, a, sa, lm=256, ln=256)

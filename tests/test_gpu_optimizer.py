@@ -265,3 +265,67 @@ def test_fused_adamw_matches_torch_adamw(cuda_device, pdtype):
     opt.step()
     check_status()
     assert torch.all(v < 0) and len(opt.param_groups) == 2
+
+
+def test_captured_graphs_survive_reallocated_gradients(cuda_device):
+    """``backward()`` + ``zero_grad()`` with PyTorch's default ``set_to_none=True`` give every step freshly
+    allocated gradients.  The captured Newton-Schulz graphs are keyed by shape and settings only (they
+    read a static update buffer), so their number stays at the number of shape groups, and the graphed
+    optimizer follows the eager one bit for bit."""
+    torch.manual_seed(7)
+    def model():
+        torch.manual_seed(7)
+        return torch.nn.Sequential(torch.nn.Linear(256, 128, bias=False), torch.nn.GELU(),
+                                   torch.nn.Linear(128, 128, bias=False), torch.nn.GELU(),
+                                   torch.nn.Linear(128, 128, bias=False), torch.nn.Linear(128, 64, bias=False)).to(cuda_device)
+    nets = [model(), model()]
+    opts = [Muon(nets[0].parameters(), lr=0.01, precision="int8_bq", use_cuda_graph=False),
+            Muon(nets[1].parameters(), lr=0.01, precision="int8_bq", use_cuda_graph=True)]
+    inputs = torch.randn(10, 16, 256, device=cuda_device)
+    keep = []          # hold on to old gradients so that new ones cannot land on the same addresses
+    for step in range(10):
+        for net, opt in zip(nets, opts):
+            net(inputs[step]).square().mean().backward()
+            keep.extend(p.grad for p in net.parameters())
+            opt.step()
+            opt.zero_grad()                      # default: set_to_none=True
+        assert len(opts[1]._ns_graphs) == 3      # 256x128, 128x128 (two matrices, one call), 128x64
+    check_status()
+    for p, q in zip(nets[0].parameters(), nets[1].parameters()):
+        assert torch.equal(p, q)
+    assert len({g.data_ptr() for g in keep}) == len(keep)
+
+
+def test_captured_graph_cache_is_bounded(cuda_device, monkeypatch):
+    from i8muon_b200 import optimizer as module
+    monkeypatch.setattr(module, "MAX_CAPTURED_GRAPHS", 2)
+    params = [torch.nn.Parameter(torch.randn(64 + 16 * i, 128, device=cuda_device) * 0.02) for i in range(4)]
+    for p in params:
+        p.grad = torch.randn_like(p) * 1e-3
+    opt = Muon(params, lr=0.01, precision="float16", use_cuda_graph=True)
+    opt.step()
+    opt.step()
+    check_status()
+    assert len(opt._ns_graphs) == 2
+
+
+def test_a_reported_status_word_raises_at_the_next_step(cuda_device):
+    """A kernel that gave up a wait writes a code to the status word.  ``step()`` copies the word to pinned
+    memory when it ends and looks at the copy when the next step begins, without a synchronisation in
+    between; here the word is set by the test itself (no kernel is made to time out)."""
+    from i8muon_b200.engine import status_word
+    p = torch.nn.Parameter(torch.randn(64, 128, device=cuda_device) * 0.02)
+    p.grad = torch.randn_like(p) * 1e-3
+    opt = Muon([p], lr=0.01, precision="float16")
+    opt.step()
+    torch.cuda.synchronize()
+    opt.step()                                   # clean word: nothing raised
+    status_word(cuda_device).fill_(0x2007)       # what an epilogue timeout of CTA 7 would leave
+    opt.step()                                   # this step ends by posting the word
+    torch.cuda.synchronize()
+    with pytest.raises(native.NativeError, match="0x2007"):
+        opt.step()
+    torch.cuda.synchronize()
+    assert int(status_word(cuda_device).item()) == 0
+    opt.step()                                   # cleared: training can go on (or stop) by the caller's choice
+    check_status()

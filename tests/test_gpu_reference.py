@@ -1,0 +1,335 @@
+"""This library's CUDA kernels against the REFERENCE'S OWN KERNELS, through the C ABI.
+
+Two sources of the reference's tensors:
+
+  * the committed fixtures ``tests/golden/reference_ns_*.npz`` (recorded on a B200 from the reference's
+    ``csrc/{int8,prec,bq}.cu`` built for sm_100a): every stage kernel here is fed the reference's inputs
+    of that stage and must reproduce its outputs - bit for bit for every integer artefact, scale,
+    diagonal and FP32 tile of the INT8 routes;
+  * the reference itself, when its build travels with the source tree (``oracle/_ref``; the tests skip
+    when it does not): the same stage-by-stage comparison at sizes where every persistent CTA walks
+    several tiles (more than 148 tiles per launch), and whole entry points at the stated tolerances.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import gpu_helpers as H
+import ref_fixtures as rf
+from i8muon_b200 import CutlassNSInt8, recommend_coefficients
+from oracle import ns_oracle as o
+from oracle import reference_gpu
+
+pytestmark = pytest.mark.gpu
+C5 = recommend_coefficients(5)
+F32 = np.float32
+
+
+def rel(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return ((a - b).norm() / b.norm()).item()
+
+
+def ulps(a, b):
+    """Distance in units of the last place between two FP32 tensors of equal sign pattern."""
+    return (a.contiguous().view(torch.int32) - b.contiguous().view(torch.int32)).abs()
+
+
+# ------------------------------------------------------------------ stage replay, shared by both sources
+def replay_int8(dev, x, calls, y_final):
+    """calls: [(op, args)] of the reference's global-INT8 driver in order (int8.cu entry points)."""
+    batch = x.reshape(-1, *x.shape[-2:]).shape[0]
+    x3 = x.reshape(batch, *x.shape[-2:]).to(dev)
+    counts = {"canonical": 0, "other": 0, "ops": set()}
+    for op, a in calls:
+        a = [t.to(dev) if isinstance(t, torch.Tensor) else t for t in a]
+        counts["ops"].add(op)
+        if op == "stats":
+            _, amax = H.stats(x3)
+            assert torch.equal(amax, a[1][0])
+        elif op == "input_quant":
+            _, maxima, norm, a8, a8t, a_scale = a[:6]
+            mine8, mine8t, mine_scale = H.input_quant(x3, maxima[0].contiguous(), norm, a[8])
+            assert torch.equal(mine8, a8) and torch.equal(mine8t, a8t) and torch.equal(mine_scale, a_scale)
+        elif op == "aat":
+            a8, g32, maxima, lm, _, slot = a
+            mine, gmax = H.i8_gemm(0, a8, a8, lm=lm, ln=lm)
+            blk = torch.arange(a8.shape[1], device=dev) // 128
+            computed = blk[:, None] >= blk[None, :]      # both implementations fill lower 128-tiles only
+            assert torch.equal(mine[:, computed], g32[:, computed])
+            assert torch.equal(gmax, maxima[slot].view(torch.int32))
+        elif op == "symmetric_quant":
+            inp, maxima, oscale, odiag, out8, scale, diag, quad, c0, c1, c2, slot = a
+            mx = maxima[slot].contiguous()
+            mine8, mine_scale, mine_diag = H.symmetric_quant(inp if quad else inp.view(torch.int32),
+                                                             mx if quad else mx.view(torch.int32), oscale,
+                                                             odiag if quad else None, bool(quad), (c0, c1, c2))
+            assert torch.equal(mine8, out8) and torch.equal(mine_scale, scale) and torch.equal(mine_diag, diag)
+        elif op == "square":
+            g8, gs, gd, p32, maxima, lm, cb, cc, _, slot = a
+            mine, pmax = H.i8_gemm(1, g8, g8, a_scale=gs, diag=gd, lm=lm, ln=lm, alpha=cb, beta=cc)
+            blk = torch.arange(g8.shape[1], device=dev) // 128
+            computed = (blk[:, None] >= blk[None, :]) & (torch.arange(g8.shape[1], device=dev) < lm)[:, None] \
+                & (torch.arange(g8.shape[1], device=dev) < lm)[None, :]
+            # the reference's binary mixes two contraction variants of this one expression, 1 ulp apart
+            d = ulps(mine[:, computed], p32[:, computed])
+            assert int(d.max()) <= 1
+            counts["canonical"] += int((d == 0).sum())
+            counts["other"] += int((d != 0).sum())
+            assert bool(((pmax.view(torch.int32) - maxima[slot].view(torch.int32)).abs() <= 1).all())
+        elif op == "update":
+            p8, ps, pd, a8t, as_, out, maxima, lm, hm, final, tr, _, a8, slot = a
+            if final:
+                mine, _ = H.i8_gemm(2, p8, a8t, row_b=a8, a_scale=ps, b_scale=as_, diag=pd, lm=lm, ln=hm,
+                                    final=True, transpose=bool(tr), out_dtype=y_final.dtype)
+                assert torch.equal(mine.cpu(), y_final.reshape(mine.shape).cpu())
+            else:
+                mine, ymax = H.i8_gemm(2, p8, a8t, row_b=a8, a_scale=ps, b_scale=as_, diag=pd, lm=lm, ln=hm)
+                assert torch.equal(mine[:, :lm, :hm], out[:, :lm, :hm])
+                assert torch.equal(ymax, maxima[slot])
+        elif op == "output_quant":
+            inp, maxima, o8, o8t, scale, slot = a
+            mine8, mine8t, mine_scale = H.output_quant(inp, maxima[slot].contiguous())
+            assert torch.equal(mine8, o8) and torch.equal(mine8t, o8t) and torch.equal(mine_scale, scale)
+    assert H.status_ok(dev) == 0
+    return counts
+
+
+def replay_bq(dev, x, calls, y_final, fp8):
+    batch = x.reshape(-1, *x.shape[-2:]).shape[0]
+    x3 = x.reshape(batch, *x.shape[-2:]).to(dev)
+    seen = set()
+    u8 = lambda t: None if t is None else t.view(torch.uint8)   # noqa: E731
+
+    def same_codes(mine, ref, what):
+        if not fp8:
+            assert torch.equal(mine, u8(ref)), what
+            return
+        # E4M3 partial sums are accumulated inside the tensor core in another order than the
+        # reference's mma.sync tiles: a few codes on a rounding edge may move by one step
+        differ = mine != u8(ref)
+        assert differ.float().mean().item() < 0.02, what
+        a, b = H.decode_q(mine, True), H.decode_q(u8(ref), True)
+        assert bool(((a - b).abs()[differ] <= 0.126 * b.abs()[differ] + 2 ** -9).all()), what
+
+    def same_floats(mine, ref, what):
+        if fp8:
+            assert torch.allclose(mine, ref, rtol=2e-5, atol=1e-9), what
+        else:
+            assert torch.equal(mine, ref), what
+
+    for op, a in calls:
+        a = [t.to(dev) if isinstance(t, torch.Tensor) else t for t in a]
+        if op == "quant":
+            inp, norm, out, out_t, scale, tr, eps = a
+            src = inp.reshape(batch, *inp.shape[-2:])
+            mine, mine_t, mine_scale = H.bq_quant(src, norm if eps > 0 else None, fp8, eps if eps > 0 else 1e-7)
+            assert torch.equal(mine, u8(out)) and torch.equal(mine_t, u8(out_t)) and torch.equal(mine_scale, scale)
+            seen.add("quant")
+            continue
+        A, sa, da, B, sb, rb, out, ot, so, dout, mode, lm, ln, ca, cb, cc, final, tr, _ = a
+        seen.add(mode)
+        if mode == 0:
+            gq, _, sg, dg = H.bq_gemm(fp8, 0, u8(A), sa, u8(B), sb, lm=lm, ln=ln)
+            same_codes(gq, out, "gram codes"); same_floats(sg, so, "gram scales"); same_floats(dg, dout, "gram diag")
+        elif mode == 1:
+            pq, _, sp, dp = H.bq_gemm(fp8, 1, u8(A), sa, u8(B), sb, da=da, lm=lm, ln=ln, coeffs=(ca, cb, cc))
+            same_codes(pq, out, "poly codes"); same_floats(sp, so, "poly scales"); same_floats(dp, dout, "poly diag")
+        elif final:
+            mine, *_ = H.bq_gemm(fp8, 2, u8(A), sa, u8(B), sb, da=da, row_b=u8(rb), lm=lm, ln=ln, final=True,
+                                 transpose=bool(tr), out_dtype=y_final.dtype)
+            want = y_final.reshape(mine.shape).to(dev)
+            if fp8:
+                assert rel(mine.float(), want.float()) < 1e-3
+            else:
+                assert torch.equal(mine, want)
+            seen.add("final")
+        else:
+            yq, yt, sy, _ = H.bq_gemm(fp8, 2, u8(A), sa, u8(B), sb, da=da, row_b=u8(rb), lm=lm, ln=ln)
+            same_codes(yq, out, "update codes"); same_codes(yt, ot, "update codes^T"); same_floats(sy, so, "update scales")
+    assert H.status_ok(dev) == 0
+    return seen
+
+
+# ------------------------------------------------------------------ committed fixtures
+@pytest.mark.parametrize("name", ["i8_staged_wide", "i8_staged_tall"])
+def test_int8_kernels_reproduce_the_recorded_reference_stages(cuda_device, name):
+    case = rf.Case(name)
+    calls = [(c["op"], case.args(c)) for c in case.calls]
+    counts = replay_int8(cuda_device, case.x, calls, case.y)
+    assert {"stats", "input_quant", "aat", "symmetric_quant", "square", "update", "output_quant"} <= counts["ops"]
+    assert counts["canonical"] > counts["other"]
+
+
+@pytest.mark.parametrize("name", ["bq_int8_staged", "bq_int8_staged_tall", "bq_fp8_staged"])
+def test_bq_kernels_reproduce_the_recorded_reference_stages(cuda_device, name):
+    case = rf.Case(name)
+    calls = [(c["op"], case.args(c)) for c in case.calls]
+    seen = replay_bq(cuda_device, case.x, calls, case.y, "fp8" in name)
+    assert {"quant", 0, 1, 2, "final"} <= seen
+
+
+FLOAT_CASES = [("float_regular_float32", 1e-5), ("float_regular_bfloat16", 2e-2), ("float_regular_float16", 2e-2),
+               ("float_regular_tall_bf16", 2e-2), ("float_first_row_fp16_of_fp32", 2e-2),
+               ("gram_bf16_00100", 2e-2), ("gram_fp16_00100", 2e-2), ("gram_fp32_00100", 1e-5),
+               ("gram_fp16_pe8_01010101", 2e-2), ("gram_fp16_0010010", 2e-2)]
+
+
+@pytest.mark.parametrize("name,tolerance", FLOAT_CASES)
+def test_floating_entry_points_against_the_recorded_reference_results(cuda_device, name, tolerance, monkeypatch):
+    case = rf.Case(name)
+    m = case.manifest
+    for key, value in m["env"].items():
+        monkeypatch.setenv(key, value)
+    engine = CutlassNSInt8(fp16_first=False)
+    y = getattr(engine, m["entry"])(case.x.to(cuda_device), case.coeffs, case.eps, True, m["precision"])
+    assert H.status_ok(cuda_device) == 0
+    assert rel(y.float(), case.y.float()) <= tolerance
+
+
+def test_polar_express_default_order_against_the_recorded_reference_result(cuda_device, monkeypatch):
+    """FP16 Gram + Polar Express x8, restart order 00100: the reference's own result is 0.12 from the exact
+    iteration (and 0.18 from a restatement that only accumulates differently), so this configuration is
+    held to the reference's distance from the exact FP32 iteration, not to 2e-2 from the reference."""
+    case = rf.Case("gram_fp16_pe8_default")
+    monkeypatch.delenv("I8MUON_GRAM_RESET", raising=False)
+    y = CutlassNSInt8()._gram_prec(case.x.to(cuda_device), case.coeffs, case.eps, True, "float16")
+    truth = o.ns_fp32_torch(case.x, case.coeffs)
+    assert rel(y.float(), truth.float()) <= 1.5 * rel(case.y.float(), truth.float()) + 1e-2
+    sv, sv_ref = torch.linalg.svdvals(y.float().cpu()[0]), torch.linalg.svdvals(case.y.float()[0])
+    assert abs(sv.mean().item() - sv_ref.mean().item()) < 3e-2
+
+
+def test_fp16_first_entry_points_against_the_recorded_reference_results(cuda_device):
+    """Default engine setting (first row in FP16).  The quantised rows are discontinuous, so they are
+    replayed from the reference's own first-row result (the input of its quantiser, held by the fixture):
+    INT8-BQ must then be bit-identical end to end, global INT8 within 2e-2; the first row within 2e-2."""
+    dev = cuda_device
+    for name, quantiser, bq in (("i8_fp16first", "stats", False), ("bq_int8_fp16first", "quant", True),
+                                ("bq_int8_fp16first_512x1024", "quant", True)):
+        case = rf.Case(name)
+        first = case.ops(quantiser)[0][0].reshape(case.x.shape)
+        mine_first = CutlassNSInt8()._regular_prec(case.x.to(dev), case.coeffs[:1], case.eps, True, "float16")
+        assert rel(mine_first.float(), first.float()) <= 2e-2, name
+        engine = CutlassNSInt8(fp16_first=False)
+        # rows 2..T on the reference's first row, without re-normalising (_cutlass.py:137-142)
+        from i8muon_b200 import native
+        route = native.ROUTE_BQ_INT8 if bq else native.ROUTE_INT8
+        y = _run_without_normalising(engine, route, first.to(dev), case.coeffs[1:], case.eps, 128 if bq else 16)
+        if bq:
+            assert torch.equal(y.cpu(), case.y), name
+        else:
+            assert rel(y.float(), case.y.float()) <= 2e-2, name
+        whole = (CutlassNSInt8()._regular_bq(case.x.to(dev), case.coeffs, case.eps, True, "int8_bq") if bq else
+                 CutlassNSInt8()._regular_i8(case.x.to(dev), case.coeffs, case.eps, True, "int8"))
+        assert rel(whole.float(), case.y.float()) <= 4e-2, name   # whole call: first rows differ in the last bit
+    assert H.status_ok(dev) == 0
+
+
+def _run_without_normalising(engine, route, x, coeffs, eps, alignment):
+    """The quantised rows of an fp16-first call on a given first-row result: stage calls with norm = None."""
+    dev = x.device
+    batch = x.reshape(-1, *x.shape[-2:]).shape[0]
+    x3 = x.reshape(batch, *x.shape[-2:]).contiguous()
+    rows, cols = x3.shape[1:]
+    l, h, lp, hp, tr = H.geometry(rows, cols, alignment)
+    from i8muon_b200 import native
+    if route == native.ROUTE_BQ_INT8:
+        a, at, sa = H.bq_quant(x3, None, False)
+        for t, (ca, cb, cc) in enumerate(coeffs):
+            gq, _, sg, dg = H.bq_gemm(False, 0, a, sa, a, sa, lm=l, ln=l)
+            pq, _, sp, dp = H.bq_gemm(False, 1, gq, sg, gq, sg, da=dg, lm=l, ln=l, coeffs=(ca, cb, cc))
+            if t == len(coeffs) - 1:
+                y, *_ = H.bq_gemm(False, 2, pq, sp, at, sa, da=dp, row_b=a, lm=l, ln=h, final=True, transpose=bool(tr),
+                                  out_dtype=x.dtype)
+                return y.reshape(x.shape)
+            a, at, sa, _ = H.bq_gemm(False, 2, pq, sp, at, sa, da=dp, row_b=a, lm=l, ln=h)
+    _, amax = H.stats(x3)
+    a8, a8t, a_scale = H.input_quant(x3, amax, None)
+    for t, (ca, cb, cc) in enumerate(coeffs):
+        g32, gmax = H.i8_gemm(0, a8, a8, lm=l, ln=l)
+        g8, g_scale, g_diag = H.symmetric_quant(g32, gmax, a_scale, None, False)
+        p32, pmax = H.i8_gemm(1, g8, g8, a_scale=g_scale, diag=g_diag, lm=l, ln=l, alpha=cb, beta=cc)
+        p8, p_scale, p_diag = H.symmetric_quant(p32, pmax, g_scale, g_diag, True, (ca, cb, cc))
+        if t == len(coeffs) - 1:
+            y, _ = H.i8_gemm(2, p8, a8t, row_b=a8, a_scale=p_scale, b_scale=a_scale, diag=p_diag, lm=l, ln=h,
+                             final=True, transpose=bool(tr), out_dtype=x.dtype)
+            return y.reshape(x.shape)
+        yf, ymax = H.i8_gemm(2, p8, a8t, row_b=a8, a_scale=p_scale, b_scale=a_scale, diag=p_diag, lm=l, ln=h)
+        a8, a8t, a_scale = H.output_quant(yf, ymax)
+
+
+# ------------------------------------------------------------------ the reference itself, at production sizes
+needs_reference = pytest.mark.skipif(not reference_gpu.available(),
+                                     reason="the reference's build (oracle/_ref) did not travel with this tree")
+
+
+def record_reference(entry, x, coeffs, precision, staged, fp16_first=False):
+    ref = reference_gpu.load()
+    engine = ref.CutlassNSInt8(fp16_first=fp16_first)
+    calls = []
+
+    def sink(source, op, args, kwargs):
+        if op in staged:
+            torch.cuda.synchronize()
+            calls.append((op, [a.clone() if isinstance(a, torch.Tensor) else a for a in args]))
+
+    with reference_gpu.record(sink):
+        y = getattr(engine, entry)(x, coeffs, 1e-7, True, precision)
+    torch.cuda.synchronize()
+    return y, calls
+
+
+@needs_reference
+@pytest.mark.parametrize("shape", [(1, 1536, 2048), (1, 2100, 1500)], ids=["1536x2048", "2100x1500-ragged-tall"])
+def test_int8_bq_every_stage_bit_exact_with_the_live_reference_beyond_one_tile_per_cta(cuda_device, shape):
+    """192 update tiles and K = 1536 (12 K blocks): the tile loop of the persistent kernel, its scale
+    ring and its four-K-block fast path, checked bit for bit against the reference's kernels."""
+    g = torch.Generator().manual_seed(61)
+    x = (torch.randn(shape, generator=g) * 1e-3).bfloat16().to(cuda_device)
+    y, calls = record_reference("_regular_bq", x, C5[:2], "int8_bq", ("quant", "gemm"))
+    seen = replay_bq(cuda_device, x, calls, y, False)
+    assert {"quant", 0, 1, 2, "final"} <= seen
+
+
+@needs_reference
+def test_fp8_bq_stages_with_the_live_reference_beyond_one_tile_per_cta(cuda_device):
+    g = torch.Generator().manual_seed(62)
+    x = (torch.randn((1, 1536, 2048), generator=g) * 1e-3).bfloat16().to(cuda_device)
+    y, calls = record_reference("_regular_bq", x, C5[:2], "float8_e4m3fn", ("quant", "gemm"))
+    seen = replay_bq(cuda_device, x, calls, y, True)
+    assert {"quant", 0, 1, 2, "final"} <= seen
+
+
+@needs_reference
+def test_global_int8_every_stage_bit_exact_with_the_live_reference_at_2048(cuda_device):
+    """256 Gram tiles through both tile streams of the whole-K persistent kernel."""
+    g = torch.Generator().manual_seed(63)
+    x = torch.randn((1, 2048, 2048), generator=g) * 1e-3
+    x = (x * torch.where(torch.rand(x.shape, generator=g) < 0.01, 50.0, 1.0)).to(cuda_device)
+    staged = ("stats", "input_quant", "aat", "symmetric_quant", "square", "update", "output_quant")
+    y, calls = record_reference("_regular_i8", x, C5[:2], "int8", staged)
+    counts = replay_int8(cuda_device, x, calls, y)
+    assert counts["canonical"] > counts["other"]
+
+
+@needs_reference
+@pytest.mark.parametrize("entry,precision,shape,dtype,tolerance", [
+    ("_regular_prec", "float32", (1, 1024, 4096), torch.float32, 1e-5),
+    ("_regular_prec", "bfloat16", (2, 768, 3072), torch.bfloat16, 2e-2),
+    ("_regular_prec", "float16", (1, 2048, 2048), torch.bfloat16, 2e-2),
+    ("_gram_prec", "bfloat16", (1, 1024, 8192), torch.bfloat16, 2e-2),
+    ("_gram_prec", "float16", (1, 1024, 8192), torch.float16, 2e-2),
+])
+def test_floating_entry_points_against_the_live_reference(cuda_device, entry, precision, shape, dtype, tolerance):
+    g = torch.Generator().manual_seed(64)
+    x = (torch.randn(shape, generator=g) * 0.02).to(dtype).to(cuda_device)
+    ref = reference_gpu.load()
+    want = getattr(ref.CutlassNSInt8(fp16_first=False), entry)(x, C5, 1e-7, True, precision)
+    got = getattr(CutlassNSInt8(fp16_first=False), entry)(x, C5, 1e-7, True, precision)
+    assert H.status_ok(cuda_device) == 0
+    assert rel(got.float(), want.float()) <= tolerance
+    sv, sv_ref = torch.linalg.svdvals(got.float()[0]), torch.linalg.svdvals(want.float()[0])
+    assert (sv - sv_ref).abs().max().item() < 1e-2 if tolerance > 1e-4 else (sv - sv_ref).abs().max().item() < 1e-4
