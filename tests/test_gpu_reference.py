@@ -73,12 +73,19 @@ def replay_int8(dev, x, calls, y_final):
             blk = torch.arange(g8.shape[1], device=dev) // 128
             computed = (blk[:, None] >= blk[None, :]) & (torch.arange(g8.shape[1], device=dev) < lm)[:, None] \
                 & (torch.arange(g8.shape[1], device=dev) < lm)[None, :]
-            # the reference's binary mixes two contraction variants of this one expression, 1 ulp apart
-            d = ulps(mine[:, computed], p32[:, computed])
-            assert int(d.max()) <= 1
-            counts["canonical"] += int((d == 0).sum())
-            counts["other"] += int((d != 0).sum())
-            assert bool(((pmax.view(torch.int32) - maxima[slot].view(torch.int32)).abs() <= 1).all())
+            # the reference's binary mixes two contraction variants of this one expression (1 ulp apart in
+            # the factor t): this library computes the canonical one; where the reference differs it must
+            # equal the other one, restated by the oracle
+            differ = (mine != p32) & computed
+            counts["canonical"] += int((computed & ~differ).sum())
+            counts["other"] += int(differ.sum())
+            if bool(differ.any()):
+                for b in range(g8.shape[0]):
+                    other, _ = o.i8_square(g8[b].cpu().numpy(), gs[b].item(), gd[b].cpu().numpy(), cb, cc, variant=1)
+                    where = differ[b].cpu()
+                    assert torch.equal(torch.from_numpy(other)[where], p32[b].cpu()[where])
+            ulp = (pmax.view(torch.int32) - maxima[slot].view(torch.int32)).abs()
+            assert int(ulp.max()) <= 4      # the maximum element may be one that took the other variant
         elif op == "update":
             p8, ps, pd, a8t, as_, out, maxima, lm, hm, final, tr, _, a8, slot = a
             if final:
