@@ -99,6 +99,7 @@ struct EpiBq {
   static constexpr int PROMOTE_KB = 1;
   static constexpr int NBUF = 4;           // TMEM accumulators of 128 columns
   static constexpr bool PRESET = !FP8;     // INT8: accumulators start at the bias constant
+  static constexpr bool SPLIT_TAIL = MODE != BQ_UPDATE_FINAL;   // has a split_tail() for bq_split_kernel
   static constexpr int STAGES = 4;
   static constexpr int MIN_CTAS = 1;
   // eight epilogue warps: two per scheduler, each thread owns half a row (64 columns),
@@ -200,6 +201,160 @@ struct EpiBq {
 #pragma unroll
     for (int i = 0; i < CPT / 16; ++i) p.comp[i] = comp ? comp[i] : make_uint4(0u, 0u, 0u, 0u);
     return p;
+  }
+
+  // ---------------------------------------------------------------- tile tail, split kernel
+  // The same arithmetic as tail() below, run by four dedicated warps on a tile whose FP32 totals
+  // the fold warps parked in shared memory (row pitch PARK_PITCH floats), so that the fold warps
+  // are already inside the next tile's K loop.  Thread `tid` owns tile row `tid` in the first
+  // two passes and tile column `tid` in the third:
+  //   pass 0  value = f(total, companion byte, diagonals) in place, tile maximum
+  //   pass 1  quantise row `tid`, 16-byte stores of the row-major tile
+  //   pass 2  quantise column `tid`, 16-byte stores of the transposed (update) or mirrored tile
+  // The four warps meet once per tile on an mbarrier (bounded wait), never on bar.sync.
+  static constexpr int PARK_PITCH = TILE + 4;   // floats; 16-byte aligned rows, conflict-free 16-byte accesses
+  static __device__ __forceinline__ bool split_tail(const GemmGeom& g, const Args& a, const int b, const int tm,
+                                                    const int tn, const int tid, const int it, const uint32_t park,
+                                                    Ctrl* ctrl, volatile uint32_t* abort_flag, const int mq,
+                                                    const int nq, const int kq) {
+    static_assert(MODE != BQ_UPDATE_FINAL, "the final update keeps the fused tail");
+    const int lane = tid & 31, w = tid >> 5;
+    const int row0 = tm * TILE, col0 = tn * TILE;
+    const int row = row0 + tid;
+    const bool in_rows = row < g.lm;
+    const bool diag_tile = (MODE != BQ_UPDATE) && tm == tn;
+    float drow = 0.f, stile = 0.f;
+    if constexpr (MODE != BQ_GRAM) drow = a.da[size_t(b) * g.m + row];
+    if constexpr (MODE == BQ_POLY) stile = a.sa[(size_t(b) * mq + tm) * kq + tn];
+    if constexpr (MODE == BQ_UPDATE) stile = a.sb[(size_t(b) * kq + tm) * nq + tn];
+    const uint8_t* comp = nullptr;
+    if constexpr (MODE == BQ_POLY)
+      comp = static_cast<const uint8_t*>(g.a_raw) + (size_t(b) * g.m + row) * g.k + col0;
+    if constexpr (MODE == BQ_UPDATE) comp = a.row_b + (size_t(b) * g.m + row) * g.n + col0;
+    const float* dcols = (MODE == BQ_POLY) ? a.da + size_t(b) * g.m + col0 : nullptr;
+    const uint32_t my_row = park + uint32_t(tid * PARK_PITCH) * 4u;
+
+    // ---- pass 0
+    float mx = 1e-8f;
+#pragma unroll 1
+    for (int j = 0; j < TILE / 16; ++j) {
+      uint32_t words[4] = {0u, 0u, 0u, 0u};
+      if constexpr (MODE != BQ_GRAM) {
+        const uint4 cw = *reinterpret_cast<const uint4*>(comp + 16 * j);
+        words[0] = cw.x; words[1] = cw.y; words[2] = cw.z; words[3] = cw.w;
+      }
+      float vals[16];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 x = lds128(my_row + uint32_t(16 * j + 4 * q4) * 4u);
+        vals[4 * q4] = x.x; vals[4 * q4 + 1] = x.y; vals[4 * q4 + 2] = x.z; vals[4 * q4 + 3] = x.w;
+      }
+      float dc[16];
+      if constexpr (MODE == BQ_POLY) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(dcols + 16 * j + 4 * q4);
+          dc[4 * q4] = d4.x; dc[4 * q4 + 1] = d4.y; dc[4 * q4 + 2] = d4.z; dc[4 * q4 + 3] = d4.w;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const int c = 16 * j + e;            // column inside the tile
+        const int col = col0 + c;
+        float val = vals[e];
+        if constexpr (MODE == BQ_GRAM) {
+          if (diag_tile && c == tid) {
+            a.dout[size_t(b) * g.m + row] = in_rows ? val : 0.f;
+            val = 0.f;
+          }
+        } else {
+          const uint8_t q = uint8_t(words[e >> 2] >> (8 * (e & 3)));
+          if constexpr (MODE == BQ_POLY) {
+            const float v = __fmul_rn(bq_decode<FP8>(q), stile);
+            val = __fmaf_rn(__fadd_rn(drow, dc[e]), v, val);
+            val = __fmaf_rn(v, a.cb, __fmul_rn(val, a.cc));
+            if (diag_tile && c == tid) {
+              const float dpoly = __fmaf_rn(drow, __fmaf_rn(drow, a.cc, a.cb), a.ca);
+              a.dout[size_t(b) * g.m + row] = in_rows ? __fadd_rn(val, dpoly) : 0.f;
+              val = 0.f;
+            }
+          } else {
+            val = __fmaf_rn(__fmul_rn(bq_decode<FP8>(q), drow), stile, val);
+          }
+        }
+        if (!in_rows || col >= g.ln) val = 0.f;   // padding never contributes to a block scale
+        mx = fmaxf(mx, fabsf(val));
+        vals[e] = val;
+      }
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4)
+        sts128(my_row + uint32_t(16 * j + 4 * q4) * 4u,
+               make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]));
+    }
+    mx = warp_max(mx);
+    if (lane == 0) ctrl->red[w] = mx;
+    __syncwarp();
+    const uint32_t meet = smem_u32(&ctrl->tail_sync);
+    mbar_arrive_if(meet, lane == 0 ? 1u : 0u);
+    if (!mbar_wait_warp_inline(meet, uint32_t(it) & 1u, abort_flag)) return false;
+    mx = fmaxf(fmaxf(ctrl->red[0], ctrl->red[1]), fmaxf(ctrl->red[2], ctrl->red[3]));
+    const float multiplier = QMAX / mx;
+    if (tid == 0) {
+      const float scale = 1.f / multiplier;
+      a.so[(size_t(b) * mq + tm) * nq + tn] = scale;
+      if constexpr (MODE != BQ_UPDATE) a.so[(size_t(b) * mq + tn) * nq + tm] = scale;
+    }
+
+    // ---- pass 1: the row-major tile (a diagonal tile takes its upper half from the lower one)
+    uint8_t* out = static_cast<uint8_t*>(a.out);
+    uint4* orow = reinterpret_cast<uint4*>(out + (size_t(b) * g.m + row) * g.n + col0);
+    const uint32_t my_col = park + uint32_t(tid) * 4u;
+#pragma unroll 1
+    for (int j = 0; j < TILE / 16; ++j) {
+      float vals[16];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 x = lds128(my_row + uint32_t(16 * j + 4 * q4) * 4u);
+        vals[4 * q4] = x.x; vals[4 * q4 + 1] = x.y; vals[4 * q4 + 2] = x.z; vals[4 * q4 + 3] = x.w;
+      }
+      if (diag_tile && 16 * j + 15 > tid) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+          if (16 * j + e > tid) vals[e] = lds32(my_col + uint32_t((16 * j + e) * PARK_PITCH) * 4u);
+      }
+      uint32_t wv[4];
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) word |= uint32_t(bq_quant<FP8>(vals[4 * k4 + e], multiplier)) << (8 * e);
+        wv[k4] = word;
+      }
+      orow[j] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+    }
+    // ---- pass 2: column `tid` of the tile = row `tid` of the transposed / mirrored tile
+    if (!diag_tile) {
+      uint8_t* tdst = (MODE == BQ_UPDATE) ? static_cast<uint8_t*>(a.out_t) : out;
+      const int trows = (MODE == BQ_UPDATE) ? g.n : g.m;
+      const int tld = (MODE == BQ_UPDATE) ? g.m : g.n;
+      uint4* trow = reinterpret_cast<uint4*>(tdst + (size_t(b) * trows + col0 + tid) * tld + row0);
+#pragma unroll 1
+      for (int j = 0; j < TILE / 16; ++j) {
+        uint32_t wv[4];
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          uint32_t word = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float v = lds32(my_col + uint32_t((16 * j + 4 * k4 + e) * PARK_PITCH) * 4u);
+            word |= uint32_t(bq_quant<FP8>(v, multiplier)) << (8 * e);
+          }
+          wv[k4] = word;
+        }
+        trow[j] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+      }
+    }
+    return true;
   }
 
   // ---------------------------------------------------------------- tile tail

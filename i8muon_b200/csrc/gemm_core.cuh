@@ -38,6 +38,7 @@ enum StatusCode : unsigned {
   ST_PRODUCER_TIMEOUT = 0x100,
   ST_MMA_TIMEOUT = 0x200,
   ST_EPILOGUE_TIMEOUT = 0x300,
+  ST_TAIL_TIMEOUT = 0x400,
 };
 
 struct GemmGeom {
@@ -65,6 +66,9 @@ struct alignas(16) Ctrl {
   int redi[8];
   float diag[TILE];
   float red2[2][8];
+  // split-tail kernel: the tile's FP32 totals parked in shared memory (full: 8 fold warps arrive,
+  // empty: 4 tail warps arrive), and the tail warps' own rendezvous (4 arrivals)
+  unsigned long long park_full, park_empty, tail_sync, pad_;
 };
 
 struct TileCtx {

@@ -7,6 +7,7 @@
 #include "epi_float.cuh"
 #include "epi_int8.cuh"
 #include "gemm_bq_persistent.cuh"
+#include "gemm_bq_split.cuh"
 #include "gemm_wholek_persistent.cuh"
 #include "passes.cuh"
 
@@ -28,8 +29,10 @@ thread_local char g_error[512] = "";
 // selection as an argument and restores the thread's own setting when it returns.
 thread_local int g_debug_simt = 0;
 thread_local int g_wholek_persistent = 1;   // 0: one CTA per tile (variant 1 of "wholek_gemm")
-thread_local int g_bq_variant = 0;   // 0: six-stage ring, 1: four-stage ring (chosen by the host-side tuner)
-constexpr int BQ_VARIANTS = 2;
+// block-quantised GEMMs: 0 = split kernel (tail on its own warps, four-stage ring), 1 = fused tail with a
+// six-stage ring, 2 = fused tail with a four-stage ring; the host-side tuner chooses per shape
+thread_local int g_bq_variant = 0;
+constexpr int BQ_VARIANTS = 3;
 std::atomic<unsigned long long> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
@@ -177,9 +180,6 @@ int launch_bq(const void* a, const void* bt, int batch, int m, int n, int k, int
   if (batch < 1 || m < 1 || n < 1 || k < 1) return fail(I8M_E_ARGUMENT, "%s: empty problem", name);
   if (!a || !bt || !status) return fail(I8M_E_ARGUMENT, "%s: null operand or status pointer", name);
   if (sym && m != n) return fail(I8M_E_ARGUMENT, "%s: symmetric product needs m == n", name);
-  const int stages = g_bq_variant == 1 ? BQP_STAGES_ALT : BQP_STAGES;
-  const size_t SMEM = size_t(stages) * 2 * TILE_BYTES + sizeof(Ctrl) + 2 * BQP_MAX_KB * sizeof(float) +
-                      Epi::TSM_BYTES + 1024;
   GemmGeom g;
   g.batch = batch; g.m = m; g.n = n; g.k = k; g.lm = lm; g.ln = ln;
   g.tiles_m = cdiv(m, TILE); g.tiles_n = cdiv(n, TILE);
@@ -194,9 +194,23 @@ int launch_bq(const void* a, const void* bt, int batch, int m, int n, int k, int
   CUtensorMap ma, mb;
   if (int rc = make_operand_map(&ma, a, 1, k, m, batch)) return rc;
   if (int rc = make_operand_map(&mb, bt, 1, k, n, batch)) return rc;
-  auto kernel = g_bq_variant == 1 ? bq_persistent_kernel<Epi, BQP_STAGES_ALT> : bq_persistent_kernel<Epi, BQP_STAGES>;
-  CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
   const unsigned grid = unsigned(std::min<long long>(tiles, sm_count()));
+  if constexpr (Epi::SPLIT_TAIL) {
+    if (g_bq_variant == 0) {
+      constexpr size_t SMEM = bq_split_smem_bytes<Epi>();
+      auto kernel = bq_split_kernel<Epi>;
+      CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
+      kernel<<<grid, BQS_THREADS, SMEM, stream>>>(ma, mb, g, args);
+      LAUNCH_CHECK(name);
+      return 0;
+    }
+  }
+  const bool four = g_bq_variant == 2;
+  const int stages = four ? BQP_STAGES_ALT : BQP_STAGES;
+  const size_t SMEM = size_t(stages) * 2 * TILE_BYTES + sizeof(Ctrl) + 2 * BQP_MAX_KB * sizeof(float) +
+                      Epi::TSM_BYTES + 1024;
+  auto kernel = four ? bq_persistent_kernel<Epi, BQP_STAGES_ALT> : bq_persistent_kernel<Epi, BQP_STAGES>;
+  CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
   kernel<<<grid, BQP_THREADS, SMEM, stream>>>(ma, mb, g, args);
   LAUNCH_CHECK(name);
   return 0;
@@ -258,14 +272,15 @@ extern "C" int i8m_set_debug_core(int simt) {
   return 0;
 }
 extern "C" int i8m_variant_count(const char* operation) {
-  if (operation && std::strcmp(operation, "bq_gemm") == 0) return 2;
+  if (operation && std::strcmp(operation, "bq_gemm") == 0) return BQ_VARIANTS;
   if (operation && std::strcmp(operation, "wholek_gemm") == 0) return 2;
   return 0;
 }
 extern "C" int i8m_set_variant(const char* operation, int variant) {
   if (!operation || (std::strcmp(operation, "bq_gemm") != 0 && std::strcmp(operation, "wholek_gemm") != 0))
     return fail(I8M_E_ARGUMENT, "set_variant: unknown operation");
-  if (variant < 0 || variant >= 2) return fail(I8M_E_ARGUMENT, "set_variant: variants are 0 and 1");
+  if (variant < 0 || variant >= i8m_variant_count(operation))
+    return fail(I8M_E_ARGUMENT, "set_variant: %s has variants 0 to %d", operation, i8m_variant_count(operation) - 1);
   if (operation[0] == 'b') g_bq_variant = variant;
   else g_wholek_persistent = variant == 0 ? 1 : 0;
   return 0;

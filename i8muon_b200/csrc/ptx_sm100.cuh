@@ -81,6 +81,13 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
   if (__all_sync(0xffffffffu, done)) return true;
   return mbar_wait_warp_slow(bar, parity, abort_flag);
 }
+// The same, fully inlined: for warps whose register budget (setmaxnreg) differs from that of the
+// warps that call the out-of-line version - one function body cannot serve two budgets.
+__device__ __forceinline__ bool mbar_wait_warp_inline(uint32_t bar, uint32_t parity,
+                                                      volatile uint32_t* abort_flag) {
+  const bool ok = mbar_wait(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, ok);
+}
 // Arrival by the lanes whose `pred` is non-zero, as one predicated instruction.
 __device__ __forceinline__ void mbar_arrive_if(uint32_t bar, uint32_t pred) {
   asm volatile(
@@ -98,6 +105,13 @@ __device__ __forceinline__ uint4 lds128u(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, float4 v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+// two packed FP32 pairs (four consecutive floats) as one 16-byte store
+__device__ __forceinline__ void sts128_pairs(uint32_t addr, unsigned long long lo, unsigned long long hi) {
+  asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(addr), "l"(lo), "l"(hi) : "memory");
 }
 __device__ __forceinline__ void sts8(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");

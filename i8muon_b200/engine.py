@@ -147,7 +147,7 @@ class CutlassNSInt8:
             variant = 0
             if route in (native.ROUTE_BQ_INT8, native.ROUTE_BQ_FP8):
                 key = (x.device.index, x.dtype, batch, rows, cols, route, steps, bool(fp16_first))
-                variant = self._factory.select("bq_gemm", key, (0, 1), 0, launch)
+                variant = self._factory.select("bq_gemm", key, tuple(range(native.variant_count("bq_gemm"))), 0, launch)
             launch(variant)
         # The workspace may be reused by later allocations on this stream only.
         return out.view(shape)

@@ -119,6 +119,11 @@ def stats_scratch_bytes(batch, count) -> int:
     return size.value
 
 
+def variant_count(operation: str) -> int:
+    """Number of kernel variants the library offers for an operation ("bq_gemm", "wholek_gemm")."""
+    return int(library().i8m_variant_count(operation.encode()))
+
+
 def launch_count() -> int:
     return int(library().i8m_launch_count())
 

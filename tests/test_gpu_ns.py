@@ -258,27 +258,29 @@ def test_autotuned_engine_and_kernel_variants_give_identical_results(cuda_device
     x = (torch.randn((3, 256, 640), generator=g) * 0.02).bfloat16().to(cuda_device)
     plain = CutlassNSInt8()
     want = plain._regular_bq(x, C5, precision="int8_bq")
-    assert native.library().i8m_variant_count(b"bq_gemm") == 2
+    assert native.variant_count("bq_gemm") == 3    # split tail (default), fused tail with six / four stages
+    a, at, sa = H.bq_quant(x, None, False)
+    results = []
     try:
-        native.call("i8m_set_variant", b"bq_gemm", 1)
-        # the engine passes its own selection with every call, so drive the stage directly
-        a, at, sa = H.bq_quant(x, None, False)
-        native.call("i8m_set_variant", b"bq_gemm", 0)
-        g0 = H.bq_gemm(False, 0, a, sa, a, sa, lm=256, ln=256)
-        native.call("i8m_set_variant", b"bq_gemm", 1)
-        g1 = H.bq_gemm(False, 0, a, sa, a, sa, lm=256, ln=256)
+        for variant in range(3):
+            # the engine passes its own selection with every call, so drive the stages directly
+            native.call("i8m_set_variant", b"bq_gemm", variant)
+            gq, _, sg, dg = H.bq_gemm(False, 0, a, sa, a, sa, lm=256, ln=256)
+            pq, _, sp, dp = H.bq_gemm(False, 1, gq, sg, gq, sg, da=dg, lm=256, ln=256, coeffs=C5[1])
+            y, yt, sy, _ = H.bq_gemm(False, 2, pq, sp, at, sa, da=dp, row_b=a, lm=256, ln=640)
+            results.append((gq, sg, dg, pq, sp, dp, y, yt, sy))
     finally:
         native.call("i8m_set_variant", b"bq_gemm", 0)
-    for p, q in zip(g0, g1):
-        if isinstance(p, torch.Tensor):
-            assert torch.equal(p, q)   # quantised Gram tile, its scales and the FP32 diagonal
+    for other in results[1:]:
+        for p, q in zip(results[0], other):
+            assert torch.equal(p, q)   # quantised tiles, their transposes, scales and FP32 diagonals
     tuned = CutlassNSInt8(autotune=True)
     got = tuned._regular_bq(x, C5, precision="int8_bq")
     check_status()
     assert torch.equal(got, want)
     assert len(tuned._factory.timings) == 1
     (scores,) = tuned._factory.timings.values()
-    assert set(scores) == {0, 1} and all(v > 0 for v in scores.values())
+    assert set(scores) == {0, 1, 2} and all(v > 0 for v in scores.values())
     with pytest.raises(native.NativeError):
         native.call("i8m_set_variant", b"no_such_op", 0)
 

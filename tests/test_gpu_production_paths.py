@@ -68,15 +68,47 @@ def bq_iteration_bit_exact(dev, x, coeffs, fp8=False):
         assert np.array_equal(npy(yfin[i]), want), "final FP32 tile"
 
 
+@pytest.fixture(params=[0, 1, 2], ids=["split-tail", "fused-tail-6-stages", "fused-tail-4-stages"])
+def bq_variant(request):
+    """Every kernel variant of the block-quantised GEMMs that the tuner may choose."""
+    from i8muon_b200 import native
+    native.call("i8m_set_variant", b"bq_gemm", request.param)
+    yield request.param
+    native.call("i8m_set_variant", b"bq_gemm", 0)
+
+
 @pytest.mark.parametrize("shape", [(1, 1536, 2048), (1, 2100, 1500), (2, 1024, 4096)],
                          ids=["1536x2048", "2100x1500-ragged-tall", "k-v-1024x4096-b2"])
-def test_int8_bq_iteration_bit_exact_beyond_one_tile_per_cta(cuda_device, shape):
+def test_int8_bq_iteration_bit_exact_beyond_one_tile_per_cta(cuda_device, bq_variant, shape):
     """1536 x 2048: 192 update tiles on 148 CTAs, K = 1536 = 12 K blocks (tile loop it >= 1, scale ring
     parity, the (nkb & 3) == 0 fast path in the polynomial and the update).  2100 x 1500: rows > cols with
     ragged edges in both dimensions (lp = 1536, hp = 2176; the Gram runs K = 2176 = 17 K blocks, the
     general loop).  1024 x 4096 x 2: the k/v shape of the Llama-shaped set, two matrices."""
     x = seeded(shape, torch.bfloat16, 71).to(cuda_device)
     bq_iteration_bit_exact(cuda_device, x, C5[1])
+
+
+def test_e4m3_bq_iteration_beyond_one_tile_per_cta(cuda_device, bq_variant):
+    """E4M3 at 1536 x 2048 on every kernel variant: the variants must agree with each other bit for bit
+    (same tensor-core instructions in the same order), and with the oracle within one E4M3 step on the
+    few codes that sit on a rounding edge (the tensor core's accumulation order is its own)."""
+    dev = cuda_device
+    x = seeded((1, 1536, 2048), torch.bfloat16, 76).to(dev)
+    norm, _ = H.stats(x)
+    a, at, sa = H.bq_quant(x, norm, True)
+    gq, _, sg, dg = H.bq_gemm(True, 0, a, sa, a, sa, lm=1536, ln=1536)
+    pq, _, sp, dp = H.bq_gemm(True, 1, gq, sg, gq, sg, da=dg, lm=1536, ln=1536, coeffs=C5[1])
+    y, yt, sy, _ = H.bq_gemm(True, 2, pq, sp, at, sa, da=dp, row_b=a, lm=1536, ln=2048)
+    assert H.status_ok(dev) == 0
+    got = [t.cpu() for t in (gq, sg, dg, pq, sp, dp, y, yt, sy)]
+    if not hasattr(test_e4m3_bq_iteration_beyond_one_tile_per_cta, "first"):
+        test_e4m3_bq_iteration_beyond_one_tile_per_cta.first = got
+    for p, q in zip(test_e4m3_bq_iteration_beyond_one_tile_per_cta.first, got):
+        assert torch.equal(p, q)
+    w_gq, w_sg, w_dg = o.bq_gram(npy(H.decode_q(a[0], True)), npy(sa[0]), 1536, True)
+    differ = npy(H.decode_q(gq[0], True)) != w_gq
+    assert differ.mean() < 0.02 and np.allclose(npy(sg[0]), w_sg, rtol=2e-5) and np.allclose(npy(dg[0]), w_dg, rtol=2e-5)
+    assert torch.equal(yt[0], y[0].mT)
 
 
 def test_int8_bq_iteration_bit_exact_on_the_gate_projection_shape(cuda_device):
