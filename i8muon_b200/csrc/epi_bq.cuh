@@ -206,13 +206,104 @@ struct EpiBq {
   // ---------------------------------------------------------------- tile tail, split kernel
   // The same arithmetic as tail() below, run by four dedicated warps on a tile whose FP32 totals
   // the fold warps parked in shared memory (row pitch PARK_PITCH floats), so that the fold warps
-  // are already inside the next tile's K loop.  Thread `tid` owns tile row `tid` in the first
-  // two passes and tile column `tid` in the third:
-  //   pass 0  value = f(total, companion byte, diagonals) in place, tile maximum
-  //   pass 1  quantise row `tid`, 16-byte stores of the row-major tile
-  //   pass 2  quantise column `tid`, 16-byte stores of the transposed (update) or mirrored tile
+  // are already inside the next tile's K loop.  These warps share their schedulers with the fold
+  // warps, whose FP32 pipe is the busy one, so the tail is written for few instructions and keeps
+  // conversions on the conversion unit (int8 -> float, float -> int8 / e4m3), which is idle here.
+  //   pass 0  thread = tile row: value = f(total, companion byte, diagonals) in place, tile maximum
+  //           (a Gram tile away from the diagonal and the edges only needs the maximum)
+  //   pass 1  thread = tile row: quantise, 16-byte stores of the row-major tile; the codes also go
+  //           back over the start of the thread's own parked row
+  //   pass 2  thread = 4 columns x 32 rows of the same warp's rows: 4 x 4 byte transposes of the
+  //           codes, 16-byte stores of the transposed (update) or mirrored (gram / poly) tile
   // The four warps meet once per tile on an mbarrier (bounded wait), never on bar.sync.
   static constexpr int PARK_PITCH = TILE + 4;   // floats; 16-byte aligned rows, conflict-free 16-byte accesses
+
+  static __device__ __forceinline__ float code_to_float(uint32_t word, int byte) {
+    const uint32_t q = (word >> (8 * byte)) & 0xffu;
+    if constexpr (FP8) return e4m3_to_float(uint8_t(q));
+    else return float(int(int8_t(q)));            // exact; one conversion-unit instruction
+  }
+  // four values -> four codes in one word (byte i = value i); same results as bq_quant
+  static __device__ __forceinline__ uint32_t quant4(float x0, float x1, float x2, float x3, float multiplier) {
+    if constexpr (FP8) {
+      const float2 lo = make_float2(fmaxf(-448.f, __fmul_rn(x0, multiplier)), fmaxf(-448.f, __fmul_rn(x1, multiplier)));
+      const float2 hi = make_float2(fmaxf(-448.f, __fmul_rn(x2, multiplier)), fmaxf(-448.f, __fmul_rn(x3, multiplier)));
+      return uint32_t(__nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3)) |
+             (uint32_t(__nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3)) << 16);
+    } else {
+      // |x| <= 127 (1 + 2^-23): truncation toward zero lands in [-127, 127] without a clamp
+      const uint32_t i0 = uint32_t(__float2int_rz(__fmul_rn(x0, multiplier)));
+      const uint32_t i1 = uint32_t(__float2int_rz(__fmul_rn(x1, multiplier)));
+      const uint32_t i2 = uint32_t(__float2int_rz(__fmul_rn(x2, multiplier)));
+      const uint32_t i3 = uint32_t(__float2int_rz(__fmul_rn(x3, multiplier)));
+      return __byte_perm(__byte_perm(i0, i1, 0x0040), __byte_perm(i2, i3, 0x0040), 0x5410);
+    }
+  }
+
+  // pass 0 on 16 consecutive columns of this thread's row.  SPECIAL: the tile touches the diagonal or
+  // the logical edge of the matrix (tile-uniform), and only then are elements zeroed or set aside.
+  template <bool SPECIAL>
+  static __device__ __forceinline__ float split_values16(const GemmGeom& g, const Args& a, const int b, const int row,
+                                                         const int col0, const int tid, const int j, const bool in_rows,
+                                                         const bool diag_tile, const float drow, const float stile,
+                                                         const uint8_t* comp, const float* dcols, const uint32_t my_row,
+                                                         float mx) {
+    float vals[16];
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const float4 x = lds128(my_row + uint32_t(16 * j + 4 * q4) * 4u);
+      vals[4 * q4] = x.x; vals[4 * q4 + 1] = x.y; vals[4 * q4 + 2] = x.z; vals[4 * q4 + 3] = x.w;
+    }
+    if constexpr (MODE == BQ_GRAM && !SPECIAL) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) mx = fmaxf(mx, fabsf(vals[e]));
+      return mx;                                   // nothing changes: no write-back
+    }
+    uint32_t words[4] = {0u, 0u, 0u, 0u};
+    if constexpr (MODE != BQ_GRAM) {
+      const uint4 cw = *reinterpret_cast<const uint4*>(comp + 16 * j);
+      words[0] = cw.x; words[1] = cw.y; words[2] = cw.z; words[3] = cw.w;
+    }
+    float dc[16];
+    if constexpr (MODE == BQ_POLY) {
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 d4 = *reinterpret_cast<const float4*>(dcols + 16 * j + 4 * q4);
+        dc[4 * q4] = d4.x; dc[4 * q4 + 1] = d4.y; dc[4 * q4 + 2] = d4.z; dc[4 * q4 + 3] = d4.w;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const int c = 16 * j + e;            // column inside the tile
+      float val = vals[e];
+      if constexpr (MODE == BQ_GRAM) {
+        if (SPECIAL && diag_tile && c == tid) {
+          a.dout[size_t(b) * g.m + row] = in_rows ? val : 0.f;
+          val = 0.f;
+        }
+      } else if constexpr (MODE == BQ_POLY) {
+        const float v = __fmul_rn(code_to_float(words[e >> 2], e & 3), stile);
+        val = __fmaf_rn(__fadd_rn(drow, dc[e]), v, val);
+        val = __fmaf_rn(v, a.cb, __fmul_rn(val, a.cc));
+        if (SPECIAL && diag_tile && c == tid) {
+          const float dpoly = __fmaf_rn(drow, __fmaf_rn(drow, a.cc, a.cb), a.ca);
+          a.dout[size_t(b) * g.m + row] = in_rows ? __fadd_rn(val, dpoly) : 0.f;
+          val = 0.f;
+        }
+      } else {
+        val = __fmaf_rn(__fmul_rn(code_to_float(words[e >> 2], e & 3), drow), stile, val);
+      }
+      if (SPECIAL && (!in_rows || col0 + c >= g.ln)) val = 0.f;   // padding never contributes to a block scale
+      mx = fmaxf(mx, fabsf(val));
+      vals[e] = val;
+    }
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4)
+      sts128(my_row + uint32_t(16 * j + 4 * q4) * 4u,
+             make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]));
+    return mx;
+  }
+
   static __device__ __forceinline__ bool split_tail(const GemmGeom& g, const Args& a, const int b, const int tm,
                                                     const int tn, const int tid, const int it, const uint32_t park,
                                                     Ctrl* ctrl, volatile uint32_t* abort_flag, const int mq,
@@ -223,6 +314,7 @@ struct EpiBq {
     const int row = row0 + tid;
     const bool in_rows = row < g.lm;
     const bool diag_tile = (MODE != BQ_UPDATE) && tm == tn;
+    const bool special = diag_tile || row0 + TILE > g.lm || col0 + TILE > g.ln;
     float drow = 0.f, stile = 0.f;
     if constexpr (MODE != BQ_GRAM) drow = a.da[size_t(b) * g.m + row];
     if constexpr (MODE == BQ_POLY) stile = a.sa[(size_t(b) * mq + tm) * kq + tn];
@@ -236,60 +328,14 @@ struct EpiBq {
 
     // ---- pass 0
     float mx = 1e-8f;
+    if (special) {
 #pragma unroll 1
-    for (int j = 0; j < TILE / 16; ++j) {
-      uint32_t words[4] = {0u, 0u, 0u, 0u};
-      if constexpr (MODE != BQ_GRAM) {
-        const uint4 cw = *reinterpret_cast<const uint4*>(comp + 16 * j);
-        words[0] = cw.x; words[1] = cw.y; words[2] = cw.z; words[3] = cw.w;
-      }
-      float vals[16];
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        const float4 x = lds128(my_row + uint32_t(16 * j + 4 * q4) * 4u);
-        vals[4 * q4] = x.x; vals[4 * q4 + 1] = x.y; vals[4 * q4 + 2] = x.z; vals[4 * q4 + 3] = x.w;
-      }
-      float dc[16];
-      if constexpr (MODE == BQ_POLY) {
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const float4 d4 = *reinterpret_cast<const float4*>(dcols + 16 * j + 4 * q4);
-          dc[4 * q4] = d4.x; dc[4 * q4 + 1] = d4.y; dc[4 * q4 + 2] = d4.z; dc[4 * q4 + 3] = d4.w;
-        }
-      }
-#pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        const int c = 16 * j + e;            // column inside the tile
-        const int col = col0 + c;
-        float val = vals[e];
-        if constexpr (MODE == BQ_GRAM) {
-          if (diag_tile && c == tid) {
-            a.dout[size_t(b) * g.m + row] = in_rows ? val : 0.f;
-            val = 0.f;
-          }
-        } else {
-          const uint8_t q = uint8_t(words[e >> 2] >> (8 * (e & 3)));
-          if constexpr (MODE == BQ_POLY) {
-            const float v = __fmul_rn(bq_decode<FP8>(q), stile);
-            val = __fmaf_rn(__fadd_rn(drow, dc[e]), v, val);
-            val = __fmaf_rn(v, a.cb, __fmul_rn(val, a.cc));
-            if (diag_tile && c == tid) {
-              const float dpoly = __fmaf_rn(drow, __fmaf_rn(drow, a.cc, a.cb), a.ca);
-              a.dout[size_t(b) * g.m + row] = in_rows ? __fadd_rn(val, dpoly) : 0.f;
-              val = 0.f;
-            }
-          } else {
-            val = __fmaf_rn(__fmul_rn(bq_decode<FP8>(q), drow), stile, val);
-          }
-        }
-        if (!in_rows || col >= g.ln) val = 0.f;   // padding never contributes to a block scale
-        mx = fmaxf(mx, fabsf(val));
-        vals[e] = val;
-      }
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4)
-        sts128(my_row + uint32_t(16 * j + 4 * q4) * 4u,
-               make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]));
+      for (int j = 0; j < TILE / 16; ++j)
+        mx = split_values16<true>(g, a, b, row, col0, tid, j, in_rows, diag_tile, drow, stile, comp, dcols, my_row, mx);
+    } else {
+#pragma unroll 1
+      for (int j = 0; j < TILE / 16; ++j)
+        mx = split_values16<false>(g, a, b, row, col0, tid, j, in_rows, diag_tile, drow, stile, comp, dcols, my_row, mx);
     }
     mx = warp_max(mx);
     if (lane == 0) ctrl->red[w] = mx;
@@ -322,36 +368,42 @@ struct EpiBq {
         for (int e = 0; e < 16; ++e)
           if (16 * j + e > tid) vals[e] = lds32(my_col + uint32_t((16 * j + e) * PARK_PITCH) * 4u);
       }
-      uint32_t wv[4];
-#pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) word |= uint32_t(bq_quant<FP8>(vals[4 * k4 + e], multiplier)) << (8 * e);
-        wv[k4] = word;
-      }
-      orow[j] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+      uint4 codes;
+      codes.x = quant4(vals[0], vals[1], vals[2], vals[3], multiplier);
+      codes.y = quant4(vals[4], vals[5], vals[6], vals[7], multiplier);
+      codes.z = quant4(vals[8], vals[9], vals[10], vals[11], multiplier);
+      codes.w = quant4(vals[12], vals[13], vals[14], vals[15], multiplier);
+      orow[j] = codes;
+      // the codes of columns 16j .. 16j+15 go over floats 4j .. 4j+3 of this row, which this thread has
+      // read already (chunk j / 4); a diagonal tile has no third pass and other rows still read its floats
+      if (!diag_tile) sts128u(my_row + uint32_t(16 * j), codes);
     }
-    // ---- pass 2: column `tid` of the tile = row `tid` of the transposed / mirrored tile
+    // ---- pass 2: codes of rows 32w .. 32w+31 (this warp's own), columns 4 lane .. 4 lane + 3, transposed
     if (!diag_tile) {
+      __syncwarp();
       uint8_t* tdst = (MODE == BQ_UPDATE) ? static_cast<uint8_t*>(a.out_t) : out;
       const int trows = (MODE == BQ_UPDATE) ? g.n : g.m;
       const int tld = (MODE == BQ_UPDATE) ? g.m : g.n;
-      uint4* trow = reinterpret_cast<uint4*>(tdst + (size_t(b) * trows + col0 + tid) * tld + row0);
+      uint8_t* tbase = tdst + (size_t(b) * trows + col0 + 4 * lane) * tld + row0 + 32 * w;
+      const uint32_t src = park + uint32_t(32 * w * PARK_PITCH) * 4u + uint32_t(4 * lane);
 #pragma unroll 1
-      for (int j = 0; j < TILE / 16; ++j) {
-        uint32_t wv[4];
+      for (int half = 0; half < 2; ++half) {
+        uint32_t o[4][4];       // [column][four rows each]
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {
-          uint32_t word = 0;
+        for (int blk = 0; blk < 4; ++blk) {
+          uint32_t r4[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float v = lds32(my_col + uint32_t((16 * j + 4 * k4 + e) * PARK_PITCH) * 4u);
-            word |= uint32_t(bq_quant<FP8>(v, multiplier)) << (8 * e);
-          }
-          wv[k4] = word;
+          for (int i = 0; i < 4; ++i) r4[i] = lds32u(src + uint32_t((16 * half + 4 * blk + i) * PARK_PITCH) * 4u);
+          const uint32_t t0 = __byte_perm(r4[0], r4[1], 0x5140), t1 = __byte_perm(r4[2], r4[3], 0x5140);
+          const uint32_t t2 = __byte_perm(r4[0], r4[1], 0x7362), t3 = __byte_perm(r4[2], r4[3], 0x7362);
+          o[0][blk] = __byte_perm(t0, t1, 0x5410);
+          o[1][blk] = __byte_perm(t0, t1, 0x7632);
+          o[2][blk] = __byte_perm(t2, t3, 0x5410);
+          o[3][blk] = __byte_perm(t2, t3, 0x7632);
         }
-        trow[j] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<uint4*>(tbase + size_t(c) * tld + 16 * half) = make_uint4(o[c][0], o[c][1], o[c][2], o[c][3]);
       }
     }
     return true;
