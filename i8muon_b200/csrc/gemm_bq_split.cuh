@@ -7,8 +7,8 @@
 // memory (16 vector stores per thread) and go straight into the next tile's K loop, and a fourth
 // warpgroup does the tail from the parked tile while that K loop runs.
 //
-//   warpgroup 0   warps 0/2 TMA producers, warps 1/3 tcgen05.mma issuers      (56 registers)
-//   warpgroups 1-2  eight fold warps, as in bq_persistent_kernel               (192 registers)
+//   warpgroup 0   warps 0/2 TMA producers, warps 1/3 tcgen05.mma issuers      (40 registers)
+//   warpgroups 1-2  eight fold warps, as in bq_persistent_kernel               (200 registers)
 //   warpgroup 3   four tail warps: EpiBq::split_tail                           (72 registers)
 //
 // Shared memory: a four-stage operand ring (128 KB), the parked tile (66 KB), the scale ring.
@@ -23,8 +23,8 @@ namespace i8m {
 
 constexpr int BQS_STAGES = 4;
 constexpr int BQS_THREADS = 512;
-constexpr int BQS_CTRL_REGS = 56;
-constexpr int BQS_FOLD_REGS = 192;
+constexpr int BQS_CTRL_REGS = 40;
+constexpr int BQS_FOLD_REGS = 200;
 constexpr int BQS_TAIL_REGS = 72;
 static_assert(128 * BQS_CTRL_REGS + 256 * BQS_FOLD_REGS + 128 * BQS_TAIL_REGS <= 65536, "register file");
 
