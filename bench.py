@@ -1,6 +1,10 @@
 """Benchmark of the Muon step over a Llama-3-8B-shaped parameter set on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference|reference-gpu]
+                    [--config cfg4-int8bq|cfg4-fp8bq|cfg1|cfg2|cfg2-gram|cfg3|cfg5]
+
+The default configuration (cfg4-int8bq) is the headline below; the others are the remaining
+configurations of the baseline list, each timed through the drop-in ``Muon(...).step()``.
 
 One "step" is one full optimizer step (momentum, Newton-Schulz, weight decay and
 update) over 224 synthetic matrices: 32 layers x {q 4096x4096, k 1024x4096,
@@ -119,7 +123,7 @@ def cpu_sample_step(sample, coeffs):
 
 def make_cpu_sample():
     gen = torch.Generator().manual_seed(4000)
-    sample_shapes = [(1024, 4096), (4096, 4096)]
+    sample_shapes = [(1024, 4096), (4096, 4096), (14336, 4096), (4096, 14336)]   # one matrix per distinct shape
     sample = []
     for s in sample_shapes:
         p = (torch.randn(s, generator=gen) * 0.02).bfloat16()
@@ -141,8 +145,8 @@ def time_cpu(steps: int, warmup: int):
     seconds = (time.perf_counter() - start) / steps
     flops = ns_flops_of(sample_shapes)
     return {"value": flops / seconds / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": "one k (1024x4096) and one q (4096x4096) matrix per step, FP32 torch NS, "
-                      f"{flops:.3e} flop, {seconds:.2f} s/step", "seconds_per_step": seconds}
+            "sample": "one matrix per distinct shape per step (k 1024x4096, q 4096x4096, gate 14336x4096, down "
+                      f"4096x14336), FP32 torch NS, {flops:.3e} flop, {seconds:.2f} s/step", "seconds_per_step": seconds}
 
 
 def config_dict(world: int, layers: int, precision: str, fp16_first: bool):
@@ -225,9 +229,198 @@ def reference_gpu_leg(args):
     try:
         done = subprocess.run(command, capture_output=True, text=True, timeout=600)
         lines = [ln for ln in done.stdout.splitlines() if ln.startswith("{")]
-        return json.loads(lines[-1]) if lines else {"unavailable": (done.stderr or "no output")[-300:]}
+        if not lines:
+            return {"unavailable": (done.stderr or "no output")[-300:]}
+        full = json.loads(lines[-1])
+        return {k: full[k] for k in ("value", "unit", "ms_per_step", "steps", "what", "gpu", "unavailable") if k in full}
     except (subprocess.TimeoutExpired, json.JSONDecodeError) as err:
         return {"unavailable": str(err)[-300:]}
+
+
+# ----------------------------------------------------------------------------- the other configurations
+def gram_flops(l, h, steps, order="00100"):
+    """Algorithmic flops of the Gram-space iteration with restart string ``order``
+    (the products of src/i8muon/_cutlass_prec.py:111-130, dense count)."""
+    order = order + "0" * max(0, steps - len(order))
+    wide, square = 2.0 * l * l * h, 2.0 * l ** 3
+    total = wide                                             # final Q0 * A
+    for t in range(steps):
+        kind = order[t]
+        refresh = t + 1 < steps and order[t + 1] == "0"
+        if kind == "1":
+            total += wide                                    # A <- Q0 * A
+        total += (wide + square) if (kind == "1" or t == 0) else 2 * square
+        if refresh:
+            total += 2 * square
+    return total
+
+
+def other_config(name):
+    """Synthetic stand-ins for the baseline configurations other than the headline one: shapes,
+    dtypes and value distributions as the configuration states them, seeded."""
+    from i8muon_b200 import recommend_coefficients
+    bf16, f32 = torch.bfloat16, torch.float32
+    if name == "cfg1":
+        return dict(shapes=[(1024, 4096)], pdtype=f32, gdtype=f32, pstd=1.0, gstd=1.0, steps=5, method="int8_safe",
+                    muon=dict(precision="float32", use_gram=False), graph=False, peak="tf32x3",
+                    what="FP32 regular NS (3 x TF32 products), one 1024x4096 matrix, int8_safe x5")
+    if name == "cfg2":
+        return dict(shapes=[(768, 3072)] * 48, pdtype=bf16, gdtype=bf16, pstd=0.02, gstd=0.02, steps=5,
+                    method="int8_safe", muon=dict(precision="bfloat16", use_gram=False), graph=True, peak="bf16",
+                    what="BF16 regular NS, 48 matrices of 768x3072 in one batched call, int8_safe x5")
+    if name == "cfg2-gram":
+        return dict(shapes=[(1024, 8192)] * 48, pdtype=bf16, gdtype=bf16, pstd=0.02, gstd=0.02, steps=5,
+                    method="int8_safe", muon=dict(precision="bfloat16", use_gram=True), graph=True, peak="bf16",
+                    gram=True, what="BF16 Gram-space NS (aspect 8 >= 5, restart order 00100), 48 matrices of 1024x8192")
+    if name == "cfg3":
+        return dict(shapes=[(4096, 4096)] * 16, pdtype=f32, gdtype=f32, pstd=0.02, gstd=1e-3, steps=6,
+                    method="int8_safe", outliers=True, muon=dict(precision="int8", use_gram=False, fp16_first=True),
+                    graph=True, peak="int8",
+                    what="global INT8 NS with FP16 first row, 16 matrices of 4096x4096 FP32, 1 % of entries x50, int8_safe x6")
+    if name == "cfg5":
+        layer = [(2048, 2048)] * 4 + [(8192, 2048), (2048, 8192)]
+        return dict(shapes=layer * 24, pdtype=bf16, gdtype=bf16, pstd=0.02, gstd=1e-3, steps=8, method="polar_express",
+                    muon=dict(precision="float16", use_gram=True, gram_aspect_threshold=4.0, weight_decay=0.01,
+                              adjust_lr_fn="match_rms_adamw", momentum=(0.95, 0.95)),
+                    graph=True, peak="bf16", gram_shapes={(8192, 2048), (2048, 8192)}, adamw_rows=50257,
+                    what="full Muon step, FP16 NS with Polar Express x8 (Gram-space for the 8192x2048 / 2048x8192 "
+                         "matrices: gram_aspect_threshold 4.0, order 00100), 24 layers d=2048, the 50257x2048 "
+                         "embedding on the fused AdamW companion, CUDA graphs")
+    raise SystemExit(f"unknown --config {name}")
+
+
+def config_flops(cfg):
+    from i8muon_b200.sharding import ns_flops
+    total = 0.0
+    for shape in cfg["shapes"]:
+        l, h = min(shape), max(shape)
+        gram = cfg.get("gram") or shape in cfg.get("gram_shapes", ())
+        total += gram_flops(l, h, cfg["steps"]) if gram else ns_flops(shape, cfg["steps"])
+    return total
+
+
+def run_other_config(args):
+    """One of cfg1 / cfg2 / cfg2-gram / cfg3 / cfg5 through the drop-in optimizer on one GPU, or sharded by
+    flops over N GPUs (cfg5 is stated at 1/2/4/8)."""
+    import torch.distributed as dist
+    from i8muon_b200 import CutlassNSInt8, FusedAdamW, Muon, check_status, native, recommend_coefficients
+    from i8muon_b200.optimizer import native_step_ops
+    from i8muon_b200.sharding import ShardedMuonStep
+    cfg = other_config(args.config)
+    world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    gen = torch.Generator(device=dev).manual_seed(1000)
+    coeffs = recommend_coefficients(cfg["steps"], method=cfg["method"])
+
+    def draw(shape, std, dtype, outliers=False):
+        x = torch.randn(shape, device=dev, generator=gen) * std
+        if outliers:
+            x = x * torch.where(torch.rand(shape, device=dev, generator=gen) < 0.01, 50.0, 1.0)
+        return x.to(dtype)
+    params = [torch.nn.Parameter(draw(s, cfg["pstd"], cfg["pdtype"])) for s in cfg["shapes"]]
+    grads = [draw(s, cfg["gstd"], cfg["gdtype"], cfg.get("outliers", False)) for s in cfg["shapes"]]
+    muon_kw = dict(lr=LR, weight_decay=WD, momentum=MOMENTUM, adjust_lr_fn="match_rms_adamw")
+    muon_kw.update(cfg["muon"])
+    total_flops = config_flops(cfg)
+    scalar = None
+    if cfg.get("adamw_rows"):
+        table = torch.nn.Parameter(draw((cfg["adamw_rows"], 2048), 0.02, cfg["pdtype"]))
+        table.grad = draw(table.shape, 1e-3, cfg["pdtype"])
+        scalar = FusedAdamW([table], lr=1e-3)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, count):
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(count):
+            fn()
+        end.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(end)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item() / 1e3
+
+    if world == 1:
+        for p, g in zip(params, grads):
+            p.grad = g
+        opt = Muon(params, ns_coefficients=coeffs, use_cuda_graph=cfg["graph"], scalar_optimizer=scalar, **muon_kw)
+        step = opt.step
+        host = [torch.empty(g.shape, dtype=g.dtype).pin_memory().copy_(g) for g in grads]
+
+        def e2e_step():
+            for p, h in zip(params, host):
+                p.grad.copy_(h, non_blocking=True)
+            opt.step()
+            result_host.copy_(params[0].float().norm().reshape(1), non_blocking=True)
+    else:
+        engine = CutlassNSInt8(fp16_first=bool(muon_kw.pop("fp16_first", True)))
+        ops = native_step_ops(engine, ns_coefficients=coeffs, **{k: v for k, v in muon_kw.items()})
+        stepper = ShardedMuonStep([p.data for p in params], cfg["steps"], ops)
+        buffers = {i: torch.zeros_like(grads[i]) for i in stepper.plan.owned(rank)}
+        plain = [p.data for p in params]
+        host = [torch.empty(g.shape, dtype=g.dtype).pin_memory().copy_(g) for g in grads]
+
+        def step():
+            stepper.step(plain, grads, buffers)
+            if scalar is not None:
+                scalar.step()
+
+        def e2e_step():
+            stepper.step(plain, grads, buffers, host_grads=host)
+            if scalar is not None:
+                scalar.step()
+            result_host.copy_(plain[0].float().norm().reshape(1), non_blocking=True)
+    result_host = torch.empty(1, dtype=torch.float32).pin_memory()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    check_status()
+    sampler = ClockSampler(local) if rank == 0 else None
+    before = native.launch_count()
+    seconds = timed(step, args.steps)
+    launches = native.launch_count() - before
+    clocks = sampler.stop() if sampler else None
+    e2e_step()
+    e2e_seconds = timed(e2e_step, args.steps)
+    check_status()
+    if rank == 0:
+        peaks, source = measured_peaks()
+        bf16 = peaks["bf16_tflops_sustained"]
+        peak = {"bf16": bf16, "int8": 2 * bf16, "tf32x3": bf16 / 2 / 3}[cfg["peak"]]
+        value = total_flops * args.steps / seconds / 1e12
+        h2d = sum(g.numel() * g.element_size() for g in grads)
+        l2 = "flushed by the step itself: its tensors exceed L2" if h2d * 3 > 256e6 else \
+             "the step's tensors (%.0f MB) fit in L2; no flush between steps, as in a training loop" % (h2d * 3 / 1e6)
+        print(json.dumps({
+            "metric": "muon_step_ns_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": cfg["muon"]["precision"], "data": "synthetic",
+            "config": {"workload": f"{args.config}: {cfg['what']}", "matrices": len(cfg["shapes"]),
+                       "ns_steps": cfg["steps"], "api": "Muon(...).step()" if world == 1 else "ShardedMuonStep",
+                       "cuda_graph": bool(cfg["graph"]) and world == 1, "l2": l2},
+            "algorithmic_flops_per_step": total_flops,
+            "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
+                         "frac": value / world / peak, "traffic": None,
+                         "kernel": "whole step (every kernel of the configuration), dense flop count",
+                         "peak_source": {"bf16": "bf16_tflops_sustained", "int8": "2 x bf16_tflops_sustained (inferred: "
+                                         "INT8 dense rate is twice BF16)", "tf32x3": "bf16_tflops_sustained / 2 (TF32 "
+                                         "rate, inferred) / 3 (three TF32 products per FP32 product)"}[cfg["peak"]]
+                                        + f" of MEASURED_PEAKS.json ({source})"},
+            "e2e": {"value": total_flops * args.steps / e2e_seconds / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_seconds / args.steps * 1e3, "steps": args.steps},
+            "gpu_launches": launches, "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -264,13 +457,18 @@ def dominant_kernel_roofline(dev, peaks, source, b=4):
     seconds = start.elapsed_time(end) / 1e3 / n
     flops = 2.0 * lp * lp * hp * b
     achieved = flops / seconds / 1e12
-    peak = 2.0 * peaks["bf16_tflops_sustained"]
+    # the kernel is timed alone in a burst of ten launches (about 12 ms), so the burst figure is its
+    # denominator; the sustained one is reported beside it because the whole step runs power-capped
+    peak = 2.0 * peaks["bf16_tflops"]
+    sustained = 2.0 * peaks["bf16_tflops_sustained"]
     return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-            "traffic": 386.0e6 * b, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one B=1 "
-            "launch (291.2 + 94.7 MB), scaled by the batch: every batch matrix is an independent set of tiles",
-            "kernel": f"bq_persistent_kernel<EpiBq<int8, update>> B={b} 4096x14336 (k=4096)",
+            "frac_of_sustained_peak": achieved / sustained, "peak_sustained": sustained,
+            "traffic": 377.0e6 * b, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one B=1 "
+            "launch (283.5 + 93.5 MB), scaled by the batch: every batch matrix is an independent set of tiles",
+            "kernel": f"bq_split_kernel<EpiBq<int8, update>> B={b} 4096x14336 (k=4096)",
             "flops_per_launch": flops, "ms_per_launch": seconds * 1e3,
-            "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({source}); INT8 dense rate is twice BF16"}
+            "peak_source": f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({source}); there is no measured INT8 "
+                           "figure: the factor 2 is inferred from the INT8 : BF16 dense rate of the part"}
 
 
 def fp16_first_iteration_gemm(dev, peaks, source, b=2):
@@ -378,7 +576,7 @@ def run_native(args):
     def e2e_step():
         stepper.step(params, grads, buffers, host_grads=host_grads)
         result_host.copy_(params[0].float().norm().reshape(1), non_blocking=True)
-    e2e_steps = max(1, min(args.steps, 2))
+    e2e_steps = args.steps          # steady state: one untimed step fills the copy pipeline first
     e2e_step()
     e2e_seconds = timed(e2e_step, e2e_steps)
     check_status()
@@ -388,7 +586,30 @@ def run_native(args):
         dist.all_reduce(launch_total)
     peaks, source = measured_peaks()
     roofline = dominant_kernel_roofline(dev, peaks, source) if rank == 0 else None
+    drop_in = None
+    if world == 1 and not args.no_drop_in:
+        # the same step through the drop-in optimizer object, with its CUDA graphs
+        del stepper, buffers
+        from i8muon_b200 import Muon
+        wrapped = [torch.nn.Parameter(p) for p in params]
+        for p, g in zip(wrapped, grads):
+            p.grad = g
+        opt = Muon(wrapped, lr=LR, weight_decay=WD, momentum=MOMENTUM, ns_coefficients=coeffs,
+                   adjust_lr_fn="match_rms_adamw", precision=args.precision, fp16_first=bool(args.fp16_first),
+                   use_gram=False, use_cuda_graph=True)
+        for _ in range(3):
+            opt.step()
+        check_status()
+        before = native.launch_count()
+        api_seconds = timed(opt.step, args.steps)
+        check_status()
+        drop_in = {"api": "Muon(params, precision=..., use_cuda_graph=True).step()",
+                   "value": total_flops * args.steps / api_seconds / 1e12, "unit": "TFLOP/s",
+                   "ms_per_step": api_seconds / args.steps * 1e3, "captured_graphs": len(opt._ns_graphs),
+                   "launches_outside_graphs": native.launch_count() - before}
+        del opt, wrapped
     cpu = time_cpu(1, 0) if (rank == 0 and world == 1 and not args.no_cpu) else None
+    ref_gpu = reference_gpu_leg(args) if (rank == 0 and world == 1 and not args.no_reference_gpu) else None
     if rank == 0:
         value = total_flops * args.steps / seconds / 1e12
         line = {"metric": "muon_step_ns_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
@@ -403,6 +624,10 @@ def run_native(args):
                 "gpu_launches": int(launch_total.item()), "clocks": clocks, "roofline": roofline}
         if cpu is not None:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        if drop_in is not None:
+            line["drop_in_api"] = drop_in
+        if ref_gpu is not None:
+            line["reference_gpu"] = ref_gpu
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -414,11 +639,16 @@ def main():
     parser.add_argument("--steps", type=int, default=3)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("native", "reference", "reference-gpu"), default="native")
+    parser.add_argument("--config", default="cfg4-int8bq",
+                        choices=("cfg4-int8bq", "cfg4-fp8bq", "cfg1", "cfg2", "cfg2-gram", "cfg3", "cfg5"))
     parser.add_argument("--precision", default="int8_bq")
     parser.add_argument("--fp16-first", type=int, default=1)
     parser.add_argument("--layers", type=int, default=32, help="layers of the parameter set (32 = the full set)")
     parser.add_argument("--group-bytes", type=int, default=2 << 30)
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--no-drop-in", action="store_true", help="skip the Muon(...).step() leg")
+    parser.add_argument("--no-reference-gpu", action="store_true",
+                        help="skip timing the reference's own kernels on this GPU (oracle/_ref, when present)")
     parser.add_argument("--only-fp16", type=int, default=0, metavar="B",
                         help="only time the FP16 first-iteration update GEMM on B matrices (small case for ncu)")
     parser.add_argument("--only-roofline", type=int, default=0, metavar="B",
@@ -434,7 +664,11 @@ def main():
         peaks, source = measured_peaks()
         print(json.dumps(dominant_kernel_roofline(torch.device("cuda", 0), peaks, source, args.only_roofline)))
         return
-    if args.impl == "reference":
+    if args.config == "cfg4-fp8bq":
+        args.precision = "fp8_bq"
+    if args.impl == "native" and not args.config.startswith("cfg4"):
+        run_other_config(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.impl == "reference-gpu":
         run_reference_gpu(args)
