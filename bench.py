@@ -520,7 +520,13 @@ def run_native(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # The persistent GEMM kernels own every SM they run on, so the all-gather (an SM kernel) gets
+        # SMs of its own: the GEMMs launch on all but `--reserve-sms` SMs and NCCL is held to as many CTAs.
+        os.environ.setdefault("NCCL_MAX_CTAS", str(max(1, args.reserve_sms)))
         dist.init_process_group("nccl", device_id=dev)
+        if args.reserve_sms > 0:
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            native.call("i8m_set_cta_limit", sms - args.reserve_sms)
 
     shape_list = shapes(args.layers)
     total_flops = ns_flops_of(shape_list)
@@ -531,7 +537,8 @@ def run_native(args):
     gen = torch.Generator(device=dev).manual_seed(4000)  # same seed on every rank: replicated tensors
     params = [(torch.randn(s, device=dev, generator=gen) * 0.02).bfloat16() for s in shape_list]
     grads = [(torch.randn(s, device=dev, generator=gen) * 1e-3).bfloat16() for s in shape_list]
-    stepper = ShardedMuonStep(params, NS_STEPS, ops, max_group_bytes=args.group_bytes)
+    stepper = ShardedMuonStep(params, NS_STEPS, ops, max_group_bytes=args.group_bytes,
+                              adopt_parameters=bool(args.adopt))
     buffers = {i: torch.zeros_like(grads[i]) for i in stepper.plan.owned(rank)}
 
     def barrier():
@@ -562,6 +569,18 @@ def run_native(args):
     launches = native.launch_count() - launches_before
     clocks = sampler.stop() if sampler else None
     check_status()
+    phase_table = None
+    if args.phases:
+        # one more step with a pair of CUDA events around every phase of every chunk (max over ranks)
+        marks = []
+        barrier()
+        stepper.step(params, grads, buffers, phases=marks)
+        totals, _ = ShardedMuonStep.phase_milliseconds(marks)
+        names = sorted(totals)
+        values = torch.tensor([totals[n] for n in names], device=dev)
+        if world > 1:
+            dist.all_reduce(values, op=dist.ReduceOp.MAX)
+        phase_table = {n: round(v, 3) for n, v in zip(names, values.tolist())}
 
     # end to end: this step's gradients arrive from pinned host memory, a scalar comes back
     pinned = torch.empty(256 << 20, dtype=torch.bfloat16).pin_memory()
@@ -624,6 +643,11 @@ def run_native(args):
                 "gpu_launches": int(launch_total.item()), "clocks": clocks, "roofline": roofline}
         if cpu is not None:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        if phase_table is not None:
+            line["phase_ms_max_over_ranks"] = phase_table
+        if world > 1:
+            line["config"]["reserve_sms"] = args.reserve_sms
+            line["config"]["adopted_parameters"] = bool(args.adopt)
         if drop_in is not None:
             line["drop_in_api"] = drop_in
         if ref_gpu is not None:
@@ -645,6 +669,11 @@ def main():
     parser.add_argument("--fp16-first", type=int, default=1)
     parser.add_argument("--layers", type=int, default=32, help="layers of the parameter set (32 = the full set)")
     parser.add_argument("--group-bytes", type=int, default=2 << 30)
+    parser.add_argument("--reserve-sms", type=int, default=8,
+                        help="N > 1: SMs left to the all-gather (the GEMMs launch on the others)")
+    parser.add_argument("--adopt", type=int, default=1,
+                        help="N > 1: parameters live in the all-gather buffers and only their owner updates them")
+    parser.add_argument("--phases", action="store_true", help="add per-phase device times of one step to the line")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--no-drop-in", action="store_true", help="skip the Muon(...).step() leg")
     parser.add_argument("--no-reference-gpu", action="store_true",

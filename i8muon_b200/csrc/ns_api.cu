@@ -31,6 +31,7 @@ thread_local int g_debug_simt = 0;
 thread_local int g_wholek_persistent = 1;   // 0: one CTA per tile (variant 1 of "wholek_gemm")
 // block-quantised GEMMs: 0 = split kernel (tail on its own warps, four-stage ring), 1 = fused tail with a
 // six-stage ring, 2 = fused tail with a four-stage ring; the host-side tuner chooses per shape
+thread_local int g_cta_limit = 0;   // persistent GEMM kernels launch at most this many CTAs (0: one per SM)
 thread_local int g_bq_variant = 0;
 constexpr int BQ_VARIANTS = 3;
 std::atomic<unsigned long long> g_launches{0};
@@ -169,7 +170,7 @@ int sm_count() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
     counts[device] = n;
   }
-  return counts[device];
+  return g_cta_limit > 0 ? std::min(counts[device], g_cta_limit) : counts[device];
 }
 
 template <class Epi>
@@ -269,6 +270,11 @@ extern "C" const char* i8m_last_error(void) { return g_error; }
 extern "C" unsigned long long i8m_launch_count(void) { return g_launches.load(); }
 extern "C" int i8m_set_debug_core(int simt) {
   g_debug_simt = simt ? 1 : 0;
+  return 0;
+}
+extern "C" int i8m_set_cta_limit(int max_ctas) {
+  if (max_ctas < 0) return fail(I8M_E_ARGUMENT, "set_cta_limit: negative limit");
+  g_cta_limit = max_ctas;
   return 0;
 }
 extern "C" int i8m_variant_count(const char* operation) {

@@ -31,6 +31,7 @@ _SIGNATURES = {
     "i8m_set_debug_core": (c_int, [c_int]),
     "i8m_variant_count": (c_int, [c_char_p]),
     "i8m_set_variant": (c_int, [c_char_p, c_int]),
+    "i8m_set_cta_limit": (c_int, [c_int]),
     "i8m_stats_scratch_bytes": (c_int, [c_int, c_longlong, POINTER(c_size_t)]),
     "i8m_stats": (c_int, [_P, c_int, c_int, c_longlong, _P, c_size_t, _P, _P, _P]),
     "i8m_stats_static": (c_int, [_P, c_int, c_int, c_longlong, _P, _P, _P]),

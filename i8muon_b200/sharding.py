@@ -115,13 +115,26 @@ class ShardedMuonStep:
 
     ``buffers`` maps parameter index -> momentum buffer and only needs entries for
     the matrices this rank owns (``plan.owned(rank)``).
+
+    Two ways to bring the other ranks' results home:
+
+    * default: the orthogonalised updates are all-gathered and every rank applies weight decay and
+      the update to all parameters (three tensors of traffic over the whole parameter set per rank);
+    * ``adopt_parameters=True``: the parameter tensors are re-homed, once, as views into flat
+      all-gather buffers laid out ``[rank][slot]`` per shape-group chunk (``param.data`` is
+      re-pointed; values are kept).  Each rank then updates only the parameters it owns and the
+      in-place all-gather delivers every other rank's *updated parameters* straight into this rank's
+      parameter storage: no apply pass over foreign parameters, no staging copy.  Every collective of
+      a step is in flight under the kernels of the chunks after it; the step waits for them at its end.
     """
 
-    def __init__(self, params, steps: int, ops: StepOps, group=None, max_group_bytes: int = 2 << 30):
+    def __init__(self, params, steps: int, ops: StepOps, group=None, max_group_bytes: int = 2 << 30,
+                 adopt_parameters: bool = False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.ops = ops
+        self.steps = steps
         shapes = [tuple(p.shape) for p in params]
         keys = [(p.device.type, p.dtype, tuple(p.shape)) for p in params]
         self.plan = build_plan(shapes, keys, self.world, steps)
@@ -130,6 +143,32 @@ class ShardedMuonStep:
         self._copy_stream = None
         self._ns_takes_out = "out" in inspect.signature(ops.orthogonalise).parameters
         self._consumed: Dict[int, object] = {}   # chunk -> event: its gradients were read
+        self._chunk_list = self._plan_chunks(params)
+        self._flat: Dict[int, torch.Tensor] = {}
+        if adopt_parameters and self.world > 1:
+            self._adopt(params)
+
+    def _plan_chunks(self, like_tensors):
+        """(group, first slot, width, staging parity) in the order the step consumes them."""
+        out = []
+        for g in self.plan.groups:
+            like = like_tensors[g.members[0]]
+            per_matrix = like.numel() * like.element_size()
+            # bound the stacked batch: process the group's slots in column chunks
+            chunk = max(1, min(g.width, self.max_group_bytes // max(1, per_matrix)))
+            for first in range(0, g.width, chunk):
+                out.append((g, first, min(chunk, g.width - first), len(out) & 1))
+        return out
+
+    def _adopt(self, params) -> None:
+        for c, (g, first, width, _) in enumerate(self._chunk_list):
+            like = params[g.members[0]]
+            flat = torch.zeros((self.world * width, *like.shape), dtype=like.dtype, device=like.device)
+            for r in range(self.world):
+                for j, i in enumerate(g.slots[r][first:first + width]):
+                    flat[r * width + j].copy_(params[i])
+                    params[i].data = flat[r * width + j]
+            self._flat[c] = flat
 
     def _buffers_for(self, g: ShardGroup, width: int, like: torch.Tensor, parity: int):
         # two staging sets per signature: chunk n+1 is produced while chunk n is gathered and applied
@@ -141,17 +180,15 @@ class ShardedMuonStep:
             hit = self._staging[key] = (send, recv)
         return hit
 
-    def _chunks(self, grads):
-        """(group, first slot, width, staging parity) in the order the step consumes them."""
-        out = []
-        for g in self.plan.groups:
-            like = grads[g.members[0]]
-            per_matrix = like.numel() * like.element_size()
-            # bound the stacked batch: process the group's slots in column chunks
-            chunk = max(1, min(g.width, self.max_group_bytes // max(1, per_matrix)))
-            for first in range(0, g.width, chunk):
-                out.append((g, first, min(chunk, g.width - first), len(out) & 1))
-        return out
+    def _pair_for(self, width: int, like: torch.Tensor):
+        # adopted parameters: one (update, orthogonalised update) pair per signature serves every chunk,
+        # because the collective reads the parameter storage, not these
+        key = ("pair", tuple(like.shape), like.dtype, width)
+        hit = self._staging.get(key)
+        if hit is None:
+            hit = self._staging[key] = tuple(
+                torch.zeros((width, *like.shape), dtype=like.dtype, device=like.device) for _ in range(2))
+        return hit
 
     def _stream_gradients(self, chunks, grads, host_grads):
         """Queue the host-to-device copies of every chunk this rank owns on a copy stream.
@@ -186,50 +223,160 @@ class ShardedMuonStep:
                 ready.append(event)
         return ready
 
-    def step(self, params, grads, buffers, host_grads=None) -> None:
+    @staticmethod
+    def _mark(phases, chunk, name, device):
+        """Phase timing on request: a pair of CUDA events around a phase (see ``phase_milliseconds``)."""
+        if phases is None or device.type != "cuda":
+            return None
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        phases.append((chunk, name, start, end))
+        return end
+
+    def step(self, params, grads, buffers, host_grads=None, phases=None) -> None:
         """One step.  With ``host_grads`` (pinned host tensors, indexed like ``grads``) the
         gradients of the matrices this rank owns are first copied into ``grads`` on a separate
-        stream, chunk by chunk, overlapped with the kernels of the chunks before them."""
-        chunks = self._chunks(grads)
+        stream, chunk by chunk, overlapped with the kernels of the chunks before them.
+        ``phases``: a list that receives (chunk, phase, start event, end event) for every phase."""
+        chunks = self._chunk_list
         ready = self._stream_gradients(chunks, grads, host_grads) if host_grads is not None else None
         pending = []
         for c, (g, first, width, parity) in enumerate(chunks):
             like = grads[g.members[0]]
             mine = g.slots[self.rank][first:first + width]
-            send, recv = self._buffers_for(g, width, like, parity)
+            flat = self._flat.get(c)
+            if flat is not None:
+                send, ortho = self._pair_for(width, like)
+                recv = flat
+            else:
+                send, recv = self._buffers_for(g, width, like, parity)
             if mine:
                 if ready is not None and ready[c] is not None:
                     torch.cuda.current_stream(like.device).wait_event(ready[c])
+                end = self._mark(phases, c, "momentum", like.device)
                 self.ops.momentum([grads[i] for i in mine], [buffers[i] for i in mine], send)
+                if end is not None:
+                    end.record()
                 if like.device.type == "cuda":
                     # recorded on every step, streamed or not: a later streamed step must not overwrite
                     # a gradient that this step's momentum kernel is still reading
                     consumed = torch.cuda.Event()
                     consumed.record(torch.cuda.current_stream(like.device))
                     self._consumed[c] = consumed
-                if self._ns_takes_out:
+                end = self._mark(phases, c, "newton_schulz", like.device)
+                if flat is not None:
+                    if self._ns_takes_out:
+                        self.ops.orthogonalise(send[:len(mine)], out=ortho[:len(mine)])
+                        result = ortho[:len(mine)]
+                    else:
+                        result = self.ops.orthogonalise(send[:len(mine)])
+                elif self._ns_takes_out:
                     own = recv[self.rank * width:self.rank * width + len(mine)]
                     self.ops.orthogonalise(send[:len(mine)], out=own)
                 else:
                     send[:len(mine)].copy_(self.ops.orthogonalise(send[:len(mine)]))
+                if end is not None:
+                    end.record()
+                if flat is not None:
+                    # this rank's own parameters are views into `flat`: update them where they live
+                    end = self._mark(phases, c, "apply_own", like.device)
+                    self.ops.apply([params[i] for i in mine], result)
+                    if end is not None:
+                        end.record()
             if self.world > 1:
-                source = recv[self.rank * width:(self.rank + 1) * width] if self._ns_takes_out else send
+                if flat is not None or self._ns_takes_out:
+                    source = recv[self.rank * width:(self.rank + 1) * width]
+                else:
+                    source = send
                 work = dist.all_gather_into_tensor(recv, source, group=self.group, async_op=True)
             elif self._ns_takes_out:
                 work = None
             else:
                 work, recv = None, send
-            pending.append((g, first, width, recv, work))
+            pending.append((c, g, first, width, recv, work, flat is not None))
             # apply the previous chunk while this chunk's collective is in flight
-            if len(pending) > 1:
-                self._apply(params, *pending.pop(0))
+            if len(pending) > 1 and not pending[0][6]:
+                self._apply(params, phases, *pending.pop(0)[:6])
         while pending:
-            self._apply(params, *pending.pop(0))
+            entry = pending.pop(0)
+            if entry[6]:
+                if entry[5] is not None:
+                    end = self._mark(phases, entry[0], "gather_wait", grads[entry[1].members[0]].device)
+                    entry[5].wait()          # the parameters of the other ranks have landed in place
+                    if end is not None:
+                        end.record()
+            else:
+                self._apply(params, phases, *entry[:6])
 
-    def _apply(self, params, g: ShardGroup, first: int, width: int, recv, work) -> None:
+    def _apply(self, params, phases, c: int, g: ShardGroup, first: int, width: int, recv, work) -> None:
+        device = recv.device
         if work is not None:
+            end = self._mark(phases, c, "gather_wait", device)
             work.wait()
+            if end is not None:
+                end.record()
+        end = self._mark(phases, c, "apply_all", device)
         for r in range(self.world):
             theirs = g.slots[r][first:first + width]
             if theirs:
                 self.ops.apply([params[i] for i in theirs], recv[r * width:r * width + len(theirs)])
+        if end is not None:
+            end.record()
+
+    @staticmethod
+    def phase_milliseconds(phases):
+        """Sum of device milliseconds per phase name, and per (chunk, phase); synchronises."""
+        torch.cuda.synchronize()
+        totals, detail = {}, []
+        for chunk, name, start, end in phases:
+            ms = start.elapsed_time(end)
+            totals[name] = totals.get(name, 0.0) + ms
+            detail.append((chunk, name, ms))
+        return totals, detail
+
+    # ------------------------------------------------------------------ optimizer state
+    def state_dict(self, params, buffers, param_groups=None):
+        """An optimizer state dict in the layout of ``torch.optim.Optimizer.state_dict()`` as the
+        reference's ``Muon`` writes it (src/i8muon/_optimizer.py:319-336): ``state[index] =
+        {"momentum_buffer": tensor}`` for EVERY matrix, gathered from the ranks that own them, plus
+        ``param_groups``.  Every rank must call it (it is a collective); every rank receives the full dict,
+        on the CPU.  The result loads into a single-device ``Muon`` and into a sharded step of any world size."""
+        state = {}
+        for c, (g, first, width, _) in enumerate(self._chunk_list):
+            like = params[g.members[0]]
+            mine = g.slots[self.rank][first:first + width]
+            dtype = buffers[mine[0]].dtype if mine else None
+            if self.world > 1:
+                dtypes = [None] * self.world
+                dist.all_gather_object(dtypes, dtype, group=self.group)
+                dtype = next((d for d in dtypes if d is not None), like.dtype)
+            elif dtype is None:
+                dtype = like.dtype
+            send = torch.zeros((width, *like.shape), dtype=dtype, device=like.device)
+            for j, i in enumerate(mine):
+                send[j].copy_(buffers[i])
+            if self.world > 1:
+                recv = torch.empty((self.world * width, *like.shape), dtype=dtype, device=like.device)
+                dist.all_gather_into_tensor(recv, send, group=self.group)
+            else:
+                recv = send
+            for r in range(self.world):
+                for j, i in enumerate(g.slots[r][first:first + width]):
+                    state[i] = {"momentum_buffer": recv[r * width + j].detach().cpu().clone()}
+        groups = param_groups if param_groups is not None else [{"params": list(range(len(params)))}]
+        return {"state": dict(sorted(state.items())), "param_groups": groups}
+
+    def load_state_dict(self, state_dict, params, buffers) -> None:
+        """Take from a full state dict (``state_dict()`` above at any world size, or a single-device
+        ``Muon.state_dict()``) the momentum buffers of the matrices THIS rank owns; the others are
+        ignored.  ``buffers`` is filled in place (missing entries are created)."""
+        state = state_dict["state"]
+        for i in self.plan.owned(self.rank):
+            entry = state.get(i, state.get(str(i)))
+            if entry is None:
+                continue                                  # a parameter that never received a gradient
+            saved = entry["momentum_buffer"]
+            if i in buffers:
+                buffers[i].copy_(saved)
+            else:
+                buffers[i] = saved.to(params[i].device).clone()

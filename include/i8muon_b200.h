@@ -71,6 +71,12 @@ int i8m_set_debug_core(int simt);
  * and applies to the stage-level launches that thread makes afterwards; i8m_ns_run takes its own
  * selection as an argument. */
 int i8m_variant_count(const char* operation);
+/* The persistent GEMM kernels launch one CTA per SM and each CTA owns its SM's whole register file, so no
+ * other kernel can run beside them.  A multi-GPU step that overlaps a collective (an SM kernel) with the
+ * GEMMs caps their grid instead: at most max_ctas CTAs per launch (0 = one per SM), which leaves the other
+ * SMs to the collective.  Per calling thread, like the variant selection.  No counterpart in the reference
+ * (it is single-device). */
+int i8m_set_cta_limit(int max_ctas);
 int i8m_set_variant(const char* operation, int variant);
 
 /* ---- stage level: statistics ---------------------------------------------

@@ -139,3 +139,87 @@ def test_step_with_host_gradients_equals_step_with_resident_gradients():
         assert torch.equal(p, w)
     for i, b in buffers.items():
         assert torch.equal(b, want_bufs[i])
+
+
+def adopting_worker(rank, world, store_path, result_path):
+    dist.init_process_group("gloo", init_method=f"file://{store_path}", rank=rank, world_size=world)
+    try:
+        params, bufs, grads = make_problem()
+        before = [p.clone() for p in params]
+        ops = cpu_ops((0.95, 0.9), 0.02, 0.01, "base_lr", "spectral")
+        stepper = ShardedMuonStep(params, steps=5, ops=ops, max_group_bytes=2 * 24 * 40 * 2, adopt_parameters=True)
+        assert all(torch.equal(p, b) for p, b in zip(params, before))      # re-homing keeps the values
+        flats = list(stepper._flat.values())
+        assert flats and all(any(p.data_ptr() >= f.data_ptr() and p.data_ptr() < f.data_ptr() + f.numel() * f.element_size()
+                                 for f in flats) for p in params)          # every parameter lives in a gather buffer
+        buffers = {i: bufs[i] for i in stepper.plan.owned(rank)}
+        for step_grads in grads:
+            stepper.step(params, step_grads, buffers)
+        torch.save(dict(params=[p.clone() for p in params]), f"{result_path}.{rank}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_adopted_parameters_are_updated_by_their_owner_and_gathered_in_place(world):
+    """``adopt_parameters=True``: each rank applies the update only to the matrices it owns, and the in-place
+    all-gather of the parameter storage gives every rank the same parameters as the unsharded step."""
+    want_params, _ = expected()
+    with tempfile.TemporaryDirectory() as tmp:
+        store, result = os.path.join(tmp, "store"), os.path.join(tmp, "result")
+        mp.spawn(adopting_worker, args=(world, store, result), nprocs=world, join=True)
+        for rank in range(world):
+            got = torch.load(f"{result}.{rank}")
+            for p, w in zip(got["params"], want_params):
+                assert torch.equal(p, w)
+
+
+def checkpoint_worker(rank, world, store_path, result_path, phase):
+    dist.init_process_group("gloo", init_method=f"file://{store_path}.{phase}", rank=rank, world_size=world)
+    try:
+        params, bufs, grads = make_problem()
+        ops = cpu_ops((0.95, 0.9), 0.02, 0.01, "base_lr", "spectral")
+        stepper = ShardedMuonStep(params, steps=5, ops=ops, max_group_bytes=2 * 24 * 40 * 2)
+        owned = stepper.plan.owned(rank)
+        if phase == "save":
+            buffers = {i: bufs[i] for i in owned}
+            for step_grads in grads[:2]:
+                stepper.step(params, step_grads, buffers)
+            full = stepper.state_dict(params, buffers)
+            assert sorted(full["state"]) == list(range(len(params)))       # every matrix, on every rank
+            if rank == 0:
+                torch.save(dict(optimizer=full, params=params), result_path)
+        else:
+            saved = torch.load(result_path)
+            for p, q in zip(params, saved["params"]):
+                p.copy_(q)
+            buffers = {}
+            stepper.load_state_dict(saved["optimizer"], params, buffers)
+            assert sorted(buffers) == sorted(owned)                          # only what this rank owns
+            stepper.step(params, grads[2], buffers)
+            torch.save(dict(params=params, bufs=buffers), f"{result_path}.{phase}.{rank}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_state_dict_reloads_at_another_world_size_and_into_the_single_device_layout():
+    """Two steps on 2 ranks, ``state_dict()`` (gathered: ``state[i]["momentum_buffer"]`` for every matrix, the
+    layout of the reference's ``Muon.state_dict()``), reload on 3 ranks, one more step: parameters and
+    momentum equal three unsharded steps."""
+    want_params, want_bufs = expected()
+    with tempfile.TemporaryDirectory() as tmp:
+        store, result = os.path.join(tmp, "store"), os.path.join(tmp, "ckpt")
+        mp.spawn(checkpoint_worker, args=(2, store, result, "save"), nprocs=2, join=True)
+        saved = torch.load(result)["optimizer"]
+        assert set(saved) == {"state", "param_groups"} and saved["param_groups"][0]["params"] == list(range(9))
+        assert all(set(entry) == {"momentum_buffer"} for entry in saved["state"].values())
+        mp.spawn(checkpoint_worker, args=(3, store, result, "load"), nprocs=3, join=True)
+        seen = {}
+        for rank in range(3):
+            got = torch.load(f"{result}.load.{rank}")
+            for p, w in zip(got["params"], want_params):
+                assert torch.equal(p, w)
+            seen.update(got["bufs"])
+        assert sorted(seen) == list(range(9))
+        for i, b in seen.items():
+            assert torch.equal(b, want_bufs[i])
