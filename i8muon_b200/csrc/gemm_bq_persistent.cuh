@@ -44,6 +44,10 @@ __device__ __forceinline__ void bq_produce(const CUtensorMap* map_a, const CUten
                                            volatile uint32_t* abort_flag) {
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   constexpr int Q = TILE;
+  // Test hook (i8m_set_debug_core(2)): the producers issue nothing, so every consumer's bounded wait runs
+  // out, each role records its code in the status word and leaves, and the CTA frees its tensor memory.
+  // Nothing is in flight when that happens: no copy was issued and no MMA could start.
+  if (g.debug_simt & 0x100) return;
   int it = 0, kb = par, b = 0, tm = 0, tn = 0;
   while (kb >= nkb && it < my_tiles) { kb -= nkb; ++it; }
   if (it < my_tiles) decode_tile(g, int(blockIdx.x) + it * int(gridDim.x), b, tm, tn);

@@ -28,6 +28,7 @@ thread_local char g_error[512] = "";
 // from two threads) never see each other's choice.  i8m_ns_run additionally takes the
 // selection as an argument and restores the thread's own setting when it returns.
 thread_local int g_debug_simt = 0;
+thread_local int g_starve_producers = 0;   // test hook: see bq_produce
 thread_local int g_wholek_persistent = 1;   // 0: one CTA per tile (variant 1 of "wholek_gemm")
 // block-quantised GEMMs: 0 = split kernel (tail on its own warps, four-stage ring), 1 = fused tail with a
 // six-stage ring, 2 = fused tail with a four-stage ring; the host-side tuner chooses per shape
@@ -187,7 +188,7 @@ int launch_bq(const void* a, const void* bt, int batch, int m, int n, int k, int
   g.sym = sym;
   g.tiles_per_batch = sym ? g.tiles_m * (g.tiles_m + 1) / 2 : g.tiles_m * g.tiles_n;
   g.num_kb = cdiv(k, 128);
-  g.debug_simt = 0;
+  g.debug_simt = g_starve_producers ? 0x100 : 0;
   g.a_raw = a; g.b_raw = bt; g.status = status;
   const long long tiles = (long long)g.tiles_per_batch * batch;
   if (tiles > 0x7fffffffLL / 2) return fail(I8M_E_LIMIT, "%s: too many tiles", name);
@@ -269,7 +270,8 @@ extern "C" const char* i8m_build_info(void) {
 extern "C" const char* i8m_last_error(void) { return g_error; }
 extern "C" unsigned long long i8m_launch_count(void) { return g_launches.load(); }
 extern "C" int i8m_set_debug_core(int simt) {
-  g_debug_simt = simt ? 1 : 0;
+  g_debug_simt = simt == 1 ? 1 : 0;
+  g_starve_producers = simt == 2 ? 1 : 0;
   return 0;
 }
 extern "C" int i8m_set_cta_limit(int max_ctas) {
@@ -314,6 +316,25 @@ extern "C" int i8m_stats(const void* x, int dtype, int batch, long long count, v
   LAUNCH_CHECK("stats_partial");
   stats_final_kernel<<<batch, STATS_THREADS, 0, S(stream)>>>(psum, pmax, norm, amax, chunks);
   LAUNCH_CHECK("stats_final");
+  return 0;
+}
+
+// One launch, atomics, summation order not reproducible (the reference's deterministic=False path).
+extern "C" int i8m_stats_onepass(const void* x, int dtype, int batch, long long count, void* scratch,
+                                 size_t scratch_bytes, float* norm, float* amax, i8m_stream_t stream) {
+  if (!x || !scratch || batch < 1 || batch > 65535 || count < 1 || !float_dtype_ok(dtype))
+    return fail(I8M_E_ARGUMENT, "stats_onepass: bad argument");
+  if (count / STATS_CHUNK >= 0x7fffffffLL) return fail(I8M_E_LIMIT, "stats_onepass: count %lld is too large", count);
+  const int chunks = int(count / STATS_CHUNK + (count % STATS_CHUNK != 0));
+  const size_t need = size_t(3) * batch * sizeof(float);
+  if (scratch_bytes < need) return fail(I8M_E_WORKSPACE, "stats_onepass: scratch %zu < %zu bytes", scratch_bytes, need);
+  CUDA_TRY(cudaMemsetAsync(scratch, 0, need, S(stream)));
+  float* sumsq = static_cast<float*>(scratch);
+  unsigned* bits = reinterpret_cast<unsigned*>(sumsq + batch);
+  unsigned* arrived = bits + batch;
+  DISPATCH_IN(dtype, In, (stats_onepass_kernel<In><<<dim3(chunks, batch), STATS_THREADS, 0, S(stream)>>>(
+                             static_cast<const In*>(x), sumsq, bits, arrived, norm, amax, count, chunks)));
+  LAUNCH_CHECK("stats_onepass");
   return 0;
 }
 
@@ -699,6 +720,8 @@ struct Bump {
 struct NsCall {
   int route, dtype, batch, rows, cols, compute, steps, fp16_first;
   int factored = 0;   // coefficient rows are (c, p, q) of c * ((G + p I)^2 + q I)
+  int deterministic = 1;   // 0: one-pass statistics with atomics (summation order not reproducible)
+  int wholek[3] = {-1, -1, -1};   // global INT8: kernel variant of the Gram / square / update product (-1: thread's)
   const void* x;
   void* out;
   const double* coeffs;
@@ -707,6 +730,17 @@ struct NsCall {
   unsigned* status;
   cudaStream_t stream;
 };
+
+int call_stats(const NsCall& c, const void* x, int B, long long count, void* scratch, size_t sbytes, float* norm,
+               float* amax) {
+  if (c.deterministic) return i8m_stats(x, c.dtype, B, count, scratch, sbytes, norm, amax, c.stream);
+  return i8m_stats_onepass(x, c.dtype, B, count, scratch, sbytes, norm, amax, c.stream);
+}
+size_t stats_bytes(int B, long long count) {
+  size_t sbytes = 0;
+  i8m_stats_scratch_bytes(B, count, &sbytes);
+  return std::max(sbytes, size_t(3) * B * sizeof(float));   // either flavour fits
+}
 
 // A matrix in the floating compute dtype: one plane, or (hi, lo) for FP32.
 struct FMat {
@@ -735,13 +769,12 @@ int run_float(const NsCall& c, Bump& ws, bool plan, bool gram, const void* x, vo
   FMat z, q1;
   if (gram) { z = take_fmat(ws, sq, compute); q1 = take_fmat(ws, sq, compute); }
   float* norm = ws.take_n<float>(B);
-  size_t sbytes = 0;
-  i8m_stats_scratch_bytes(B, (long long)rows * cols, &sbytes);
+  const size_t sbytes = stats_bytes(B, (long long)rows * cols);
   void* scratch = ws.take(sbytes);
   if (plan) return 0;
 
   if (normalize_input) {
-    if (int rc = i8m_stats(x, c.dtype, B, (long long)rows * cols, scratch, sbytes, norm, nullptr, c.stream)) return rc;
+    if (int rc = call_stats(c, x, B, (long long)rows * cols, scratch, sbytes, norm, nullptr)) return rc;
   }
   if (int rc = i8m_normalize(x, c.dtype, normalize_input ? norm : nullptr, a.p, at.p, a.lo, at.lo,
                              compute, B, rows, cols, lp, hp, transpose, c.eps, c.stream))
@@ -830,16 +863,14 @@ int run_int8(const NsCall& c, Bump& ws, bool plan, const void* x, int steps, con
   float* maxima = ws.take_n<float>(size_t(3) * steps * B);
   float* norm = ws.take_n<float>(B);
   float* amax = ws.take_n<float>(B);
-  size_t sbytes = 0;
-  i8m_stats_scratch_bytes(B, (long long)rows * cols, &sbytes);
+  const size_t sbytes = stats_bytes(B, (long long)rows * cols);
   void* scratch = ws.take(sbytes);
   if (plan) return 0;
   if ((long long)hp * 127 * 127 > 0x7fffffffLL)
     return fail(I8M_E_LIMIT, "inner dimension can overflow the int32 accumulator");
 
   CUDA_TRY(cudaMemsetAsync(maxima, 0, size_t(3) * steps * B * sizeof(float), c.stream));
-  if (int rc = i8m_stats(x, c.dtype, B, (long long)rows * cols, scratch, sbytes,
-                         normalize_input ? norm : nullptr, amax, c.stream))
+  if (int rc = call_stats(c, x, B, (long long)rows * cols, scratch, sbytes, normalize_input ? norm : nullptr, amax))
     return rc;
   if (int rc = i8m_input_quant(x, c.dtype, amax, normalize_input ? norm : nullptr, a8, a8t, a_scale, B,
                                rows, cols, lp, hp, transpose, c.eps, c.stream))
@@ -855,17 +886,23 @@ int run_int8(const NsCall& c, Bump& ws, bool plan, const void* x, int steps, con
     float* gmax = maxima + size_t(3 * it) * B;
     float* pmax = gmax + B;
     float* ymax = pmax + B;
+    const int thread_wholek = g_wholek_persistent;
+    auto pick = [&](int op) { g_wholek_persistent = c.wholek[op] < 0 ? thread_wholek : (c.wholek[op] == 0 ? 1 : 0); };
+    struct Restore { int v; ~Restore() { g_wholek_persistent = v; } } restore{thread_wholek};
+    pick(0);
     if (int rc = i8m_i8_gemm(0, a8, a8, nullptr, work, gmax, nullptr, nullptr, nullptr, B, lp, lp, hp, l,
                              l, 0, 0, 0, 0, 0, c.status, c.stream))
       return rc;
     if (int rc = i8m_symmetric_quant(work, gmax, a_scale, nullptr, s8, g_scale, g_diag, B, lp, 0, shift, 0, 0, c.stream))
       return rc;
+    pick(1);
     if (int rc = i8m_i8_gemm(1, s8, s8, nullptr, work, pmax, g_scale, nullptr, g_diag, B, lp, lp, lp, l, l,
                              cb, cc, 0, 0, 0, c.status, c.stream))
       return rc;
     if (int rc = i8m_symmetric_quant(work, pmax, g_scale, g_diag, s8, p_scale, p_diag, B, lp, 1, ca, cb, cc, c.stream))
       return rc;
     const bool final = it == steps - 1;
+    pick(2);
     if (int rc = i8m_i8_gemm(factored ? 4 : 2, s8, a8t, a8, final ? c.out : static_cast<void*>(work), ymax, p_scale,
                              a_scale, p_diag, B, lp, hp, lp, l, h, gain, 0, final, transpose, c.dtype,
                              c.status, c.stream))
@@ -874,6 +911,74 @@ int run_int8(const NsCall& c, Bump& ws, bool plan, const void* x, int steps, con
       if (int rc = i8m_output_quant(work, ymax, a8, a8t, a_scale, B, lp, hp, c.stream)) return rc;
   }
   return 0;
+}
+
+// grouped cubics with a terminal quintic, all INT8 (src/i8muon/_cutlass_cubic.py:8-71): per cubic the
+// Gram product, its quantisation with the shifted FP32 diagonal, the update with -gain folded into
+// the right-hand scale, and the output quantisation; then the regular five stages of the last row.
+int run_int8_cubic(const NsCall& c, Bump& ws, bool plan) {
+  const int B = c.batch, rows = c.rows, cols = c.cols;
+  const int l = std::min(rows, cols), h = std::max(rows, cols);
+  const int lp = pad_to(l, 16), hp = pad_to(h, 16);
+  const int transpose = rows > cols;
+  const int cubics = c.steps - 2;
+  const size_t wide = size_t(B) * lp * hp, sq = size_t(B) * lp * lp;
+  int8_t* a8 = ws.take_n<int8_t>(wide);
+  int8_t* a8t = ws.take_n<int8_t>(wide);
+  float* work = ws.take_n<float>(wide);
+  int8_t* s8 = ws.take_n<int8_t>(sq);
+  float* a_scale = ws.take_n<float>(B);
+  float* g_scale = ws.take_n<float>(B);
+  float* p_scale = ws.take_n<float>(B);
+  float* g_diag = ws.take_n<float>(size_t(B) * lp);
+  float* p_diag = ws.take_n<float>(size_t(B) * lp);
+  const size_t slots = size_t(2) * std::max(cubics, 0) + 3;
+  float* maxima = ws.take_n<float>(slots * B);
+  float* norm = ws.take_n<float>(B);
+  float* amax = ws.take_n<float>(B);
+  const size_t sbytes = stats_bytes(B, (long long)rows * cols);
+  void* scratch = ws.take(sbytes);
+  if (plan) return 0;
+  if (cubics < 1) return fail(I8M_E_ARGUMENT, "the cubic route needs an input-gain row, cubic rows and a terminal row");
+  if ((long long)hp * 127 * 127 > 0x7fffffffLL)
+    return fail(I8M_E_LIMIT, "inner dimension can overflow the int32 accumulator");
+  const float input_gain = float(c.coeffs[0]);
+  if (!(input_gain > 0.f) || !(c.eps > 0.f)) return fail(I8M_E_ARGUMENT, "the cubic route needs positive input_gain and eps");
+  CUDA_TRY(cudaMemsetAsync(maxima, 0, slots * B * sizeof(float), c.stream));
+  if (int rc = call_stats(c, c.x, B, (long long)rows * cols, scratch, sbytes, norm, amax)) return rc;
+  clamp_divide_kernel<<<cdiv(B, 256), 256, 0, c.stream>>>(norm, B, c.eps, input_gain);
+  LAUNCH_CHECK("clamp_divide");
+  if (int rc = i8m_input_quant(c.x, c.dtype, amax, norm, a8, a8t, a_scale, B, rows, cols, lp, hp, transpose, 0.f, c.stream))
+    return rc;
+  for (int i = 0; i < cubics; ++i) {
+    const float gain = float(c.coeffs[3 * (i + 1)]), shift = float(c.coeffs[3 * (i + 1) + 1]);
+    float* gmax = maxima + size_t(2 * i) * B;
+    float* ymax = gmax + B;
+    if (int rc = i8m_i8_gemm(0, a8, a8, nullptr, work, gmax, nullptr, nullptr, nullptr, B, lp, lp, hp, l, l, 0, 0, 0, 0, 0,
+                             c.status, c.stream))
+      return rc;
+    if (int rc = i8m_symmetric_quant(work, gmax, a_scale, nullptr, s8, g_scale, g_diag, B, lp, 0, shift, 0, 0, c.stream))
+      return rc;
+    if (int rc = i8m_i8_gemm(4, s8, a8t, a8, work, ymax, g_scale, a_scale, g_diag, B, lp, hp, lp, l, h, -gain, 0, 0, 0, 0,
+                             c.status, c.stream))
+      return rc;
+    if (int rc = i8m_output_quant(work, ymax, a8, a8t, a_scale, B, lp, hp, c.stream)) return rc;
+  }
+  const double* abc = c.coeffs + 3 * (c.steps - 1);
+  float* gmax = maxima + size_t(2 * cubics) * B;
+  float* pmax = gmax + B;
+  if (int rc = i8m_i8_gemm(0, a8, a8, nullptr, work, gmax, nullptr, nullptr, nullptr, B, lp, lp, hp, l, l, 0, 0, 0, 0, 0,
+                           c.status, c.stream))
+    return rc;
+  if (int rc = i8m_symmetric_quant(work, gmax, a_scale, nullptr, s8, g_scale, g_diag, B, lp, 0, 0, 0, 0, c.stream)) return rc;
+  if (int rc = i8m_i8_gemm(1, s8, s8, nullptr, work, pmax, g_scale, nullptr, g_diag, B, lp, lp, lp, l, l, float(abc[1]),
+                           float(abc[2]), 0, 0, 0, c.status, c.stream))
+    return rc;
+  if (int rc = i8m_symmetric_quant(work, pmax, g_scale, g_diag, s8, p_scale, p_diag, B, lp, 1, float(abc[0]), float(abc[1]),
+                                   float(abc[2]), c.stream))
+    return rc;
+  return i8m_i8_gemm(2, s8, a8t, a8, c.out, nullptr, p_scale, a_scale, p_diag, B, lp, hp, lp, l, h, 0, 0, 1, transpose,
+                     c.dtype, c.status, c.stream);
 }
 
 // block-quantised NS (src/i8muon/_cutlass_bq.py:15-70)
@@ -898,13 +1003,12 @@ int run_bq(const NsCall& c, Bump& ws, bool plan, bool fp8, const void* x, int st
   float* dg = ws.take_n<float>(size_t(B) * lp);
   float* dp = ws.take_n<float>(size_t(B) * lp);
   float* norm = ws.take_n<float>(B);
-  size_t sbytes = 0;
-  i8m_stats_scratch_bytes(B, (long long)rows * cols, &sbytes);
+  const size_t sbytes = stats_bytes(B, (long long)rows * cols);
   void* scratch = ws.take(sbytes);
   if (plan) return 0;
 
   if (normalize_input)
-    if (int rc = i8m_stats(x, c.dtype, B, (long long)rows * cols, scratch, sbytes, norm, nullptr, c.stream)) return rc;
+    if (int rc = call_stats(c, x, B, (long long)rows * cols, scratch, sbytes, norm, nullptr)) return rc;
   if (int rc = i8m_bq_quant(x, c.dtype, normalize_input ? norm : nullptr, a, at, sa, fp8, B, rows, cols,
                             lp, hp, transpose, c.eps, c.stream))
     return rc;
@@ -973,6 +1077,8 @@ int ns_dispatch(const NsCall& c, Bump& ws, bool plan) {
     }
     case I8M_ROUTE_BQ_FP8:
       return run_bq(c, ws, plan, true, c.x, c.steps, c.coeffs, true);
+    case I8M_ROUTE_INT8_CUBIC:
+      return run_int8_cubic(c, ws, plan);
     default:
       return fail(I8M_E_ARGUMENT, "unknown route %d", c.route);
   }
@@ -994,7 +1100,7 @@ extern "C" int i8m_ns_workspace_bytes(int route, int batch, int rows, int cols, 
 
 extern "C" int i8m_ns_run(int route, const void* x, void* out, int dtype, int batch, int rows,
                           int cols, int compute, const double* coeffs, int steps, float eps,
-                          int fp16_first, int variants, const char* gram_order, void* workspace,
+                          int fp16_first, int deterministic, int variants, const char* gram_order, void* workspace,
                           size_t workspace_bytes, uint32_t* status, i8m_stream_t stream) {
   if (!x || !out || !coeffs || !workspace || !status) return fail(I8M_E_ARGUMENT, "ns_run: null pointer");
   if (x == out) return fail(I8M_E_ARGUMENT, "ns_run: out may not alias x");
@@ -1009,14 +1115,18 @@ extern "C" int i8m_ns_run(int route, const void* x, void* out, int dtype, int ba
   c.compute = compute; c.steps = steps; c.fp16_first = fp16_first;
   c.x = x; c.out = out; c.coeffs = coeffs; c.eps = eps; c.gram_order = gram_order;
   c.status = status; c.stream = S(stream);
+  c.deterministic = deterministic ? 1 : 0;
   Bump ws(workspace, workspace_bytes, false);
   if (variants < 0) return ns_dispatch(c, ws, false);
   // this call's own kernel selection; the thread's setting comes back whatever happens
   const int bq = variants & 0xff, wholek = (variants >> 8) & 0xff;
-  if (bq >= BQ_VARIANTS || wholek >= 2) return fail(I8M_E_ARGUMENT, "ns_run: unknown kernel variant 0x%x", variants);
+  const int wk_square = (variants >> 16) & 0xff, wk_update = (variants >> 24) & 0x7f;
+  if (bq >= BQ_VARIANTS || wholek >= 2 || wk_square >= 2 || wk_update >= 2)
+    return fail(I8M_E_ARGUMENT, "ns_run: unknown kernel variant 0x%x", variants);
   const int saved_bq = g_bq_variant, saved_wholek = g_wholek_persistent;
   g_bq_variant = bq;
   g_wholek_persistent = wholek == 0 ? 1 : 0;
+  c.wholek[0] = wholek; c.wholek[1] = wk_square; c.wholek[2] = wk_update;
   const int rc = ns_dispatch(c, ws, false);
   g_bq_variant = saved_bq;
   g_wholek_persistent = saved_wholek;

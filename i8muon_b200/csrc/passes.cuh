@@ -97,6 +97,48 @@ stats_final_kernel(const float* partial_sum, const float* partial_max, float* no
   }
 }
 
+// One-pass flavour for callers that do not ask for a reproducible summation order
+// (``deterministic=False``; the reference's fused path, src/i8muon/csrc/int8.cu:41-62 with
+// src/i8muon/_cutlass.py:189-194): every block adds its partial sum of squares to sumsq[b] with an
+// atomic, and the block that arrives last for a matrix writes norm[b] = sqrt(sum) and amax[b].
+// sumsq / amax_bits / arrived (3 x batch words) must be zero when the kernel starts.
+template <typename In>
+__global__ void __launch_bounds__(STATS_THREADS)
+stats_onepass_kernel(const In* x, float* sumsq, unsigned* amax_bits, unsigned* arrived, float* norm, float* amax,
+                     long long count, int chunks) {
+  __shared__ float sh[8];
+  const int b = blockIdx.y, chunk = blockIdx.x;
+  const In* src = x + size_t(b) * count;
+  long long base = (long long)chunk * STATS_CHUNK;
+  float s = 0.f, mx = 0.f;
+#pragma unroll 8
+  for (int i = 0; i < 32; ++i) {
+    long long idx = base + threadIdx.x + i * STATS_THREADS;
+    float v = idx < count ? load_f(src, size_t(idx)) : 0.f;
+    s = __fmaf_rn(v, v, s);
+    mx = fmaxf(mx, fabsf(v));
+  }
+  s = block_sum_256(s, sh);
+  mx = block_max_256(mx, sh);
+  if (threadIdx.x == 0) {
+    atomicAdd(sumsq + b, s);
+    atomicMax(amax_bits + b, __float_as_uint(mx));     // non-negative floats order like their bit patterns
+    __threadfence();
+    if (atomicAdd(arrived + b, 1u) == unsigned(chunks) - 1u) {
+      __threadfence();
+      if (norm) norm[b] = sqrtf(atomicAdd(sumsq + b, 0.f));
+      if (amax) amax[b] = __uint_as_float(atomicMax(amax_bits + b, 0u));
+    }
+  }
+}
+
+// norm[b] <- max(norm[b], eps) / gain: folds an input gain into the dequantisation scale of the
+// grouped-cubic route (src/i8muon/_cutlass_cubic.py:38-40).
+__global__ void clamp_divide_kernel(float* norm, int batch, float eps, float gain) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < batch) norm[b] = __fdiv_rn(fmaxf(norm[b], eps), gain);
+}
+
 // -------------------------------------------------------------- normalise
 // A = E(x * inv), A^T, zero padded to (m x n); restates src/i8muon/csrc/prec.cu:46-68.
 // For E = float the value is split into two TF32-representable planes.

@@ -10,11 +10,13 @@ same ``router``.  Each entry point is one call into the sm_100a library
 
 Differences that a caller can observe:
   * only compute capability 10.x devices are accepted;
-  * ``deterministic`` is accepted and ignored - the norm reduction is always the
-    deterministic two-pass one;
+  * ``deterministic=False`` selects one-pass statistics with atomics on every route (the reference
+    only has that flavour for global INT8); the default is the two-pass reduction in a fixed order;
   * the result is a fresh tensor, not a view into the call's workspace;
-  * ``tiles`` is validated and recorded but the kernels use one 128x128 CTA tile; ``autotune``
-    times the library's kernel variants of the block-quantised GEMMs instead (``tuning.py``).
+  * ``tiles`` selects, per product of the global-INT8 route (``aat``, ``square``, ``update``), between this
+    library's two kernels for whole-K products: the reference's tile id 4 (its TMA tile) maps to the
+    persistent TMA kernel (also the default), ids 0-3 (its cp.async tiles) to the one-CTA-per-tile kernel;
+    ``autotune`` times the library's kernel variants (``tuning.py``).
 """
 from __future__ import annotations
 
@@ -119,7 +121,8 @@ class CutlassNSInt8:
         return hit
 
     # ------------------------------------------------------------- launch
-    def _run(self, route, x, coeffs, eps, compute, alignment, spec_precision, fp16_first, out=None):
+    def _run(self, route, x, coeffs, eps, compute, alignment, spec_precision, fp16_first, out=None,
+             deterministic=True):
         coeffs = DEFAULT_COEFFICIENTS if coeffs is None else coeffs
         shape = x.shape
         batch, rows, cols, *_ = matrix_spec(tuple(shape), x.dtype, x.device, spec_precision, alignment)
@@ -140,11 +143,16 @@ class CutlassNSInt8:
             def launch(variant):
                 workspace = torch.empty(size, dtype=torch.uint8, device=x.device)
                 native.call("i8m_ns_run", route, x.data_ptr(), out.data_ptr(), dtype, batch, rows, cols,
-                            compute, array, steps, float(eps), int(bool(fp16_first)), int(variant),
+                            compute, array, steps, float(eps), int(bool(fp16_first)), int(bool(deterministic)),
+                            int(variant),
                             order.encode() if order is not None else None, workspace.data_ptr(), size,
                             status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
 
             variant = 0
+            if route in (native.ROUTE_INT8, native.ROUTE_INT8_FACTORED) and self.tiles:
+                # explicit tiles take precedence over measurements, as in the reference
+                per_op = [0 if self.tiles.get(op, 4) == 4 else 1 for op in ("aat", "square", "update")]
+                variant = (per_op[0] << 8) | (per_op[1] << 16) | (per_op[2] << 24)
             if route in (native.ROUTE_BQ_INT8, native.ROUTE_BQ_FP8):
                 key = (x.device.index, x.dtype, batch, rows, cols, route, steps, bool(fp16_first))
                 variant = self._factory.select("bq_gemm", key, tuple(range(native.variant_count("bq_gemm"))), 0, launch)
@@ -159,20 +167,23 @@ class CutlassNSInt8:
         precision = normalize_precision(precision)
         if precision not in _COMPUTE_CODES:
             raise ValueError(f"Unsupported floating-point precision: {precision}")
-        return self._run(native.ROUTE_FLOAT, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False, out)
+        return self._run(native.ROUTE_FLOAT, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False, out,
+                         deterministic)
 
     def _gram_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16", *, out=None):
         """Gram-space NS with restarts given by I8MUON_GRAM_RESET (src/i8muon/_cutlass_prec.py:107-130)."""
         precision = normalize_precision(precision)
         if precision not in _COMPUTE_CODES:
             raise ValueError(f"Unsupported floating-point precision: {precision}")
-        return self._run(native.ROUTE_GRAM, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False, out)
+        return self._run(native.ROUTE_GRAM, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False, out,
+                         deterministic)
 
     def _regular_i8(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="int8", *, block=False, out=None):
         """Global-scale INT8 NS, optionally after one FP16 iteration (src/i8muon/_cutlass.py:130-142)."""
         if block:
-            return self._run(native.ROUTE_BQ_INT8, x, coeffs, eps, native.F16, 128, "int8", self.fp16_first, out)
-        return self._run(native.ROUTE_INT8, x, coeffs, eps, native.F16, 16, "int8", self.fp16_first, out)
+            return self._run(native.ROUTE_BQ_INT8, x, coeffs, eps, native.F16, 128, "int8", self.fp16_first, out,
+                             deterministic)
+        return self._run(native.ROUTE_INT8, x, coeffs, eps, native.F16, 16, "int8", self.fp16_first, out, deterministic)
 
     # ------------------------------------------------ opt-in polynomial entry points
     def _regular_i8_factored(self, X, factor_rows, eps=1e-7, deterministic=True, *, out=None):
@@ -181,7 +192,8 @@ class CutlassNSInt8:
         factors = tuple(tuple(float(v) for v in row) for row in factor_rows)
         if not factors or any(len(row) != 3 or not all(map(math.isfinite, row)) for row in factors):
             raise ValueError("Expected nonempty finite (c,p,q) factor rows")
-        return self._run(native.ROUTE_INT8_FACTORED, X, factors, eps, native.F16, 16, "int8", self.fp16_first, out)
+        return self._run(native.ROUTE_INT8_FACTORED, X, factors, eps, native.F16, 16, "int8", self.fp16_first, out,
+                         deterministic)
 
     def _regular_i8_grouped_cubic(self, X, input_gain, cubic_gains, terminal_abc, eps=1e-7):
         """All-INT8 grouped cubics T <- -gain * (T T^T - I) T followed by one quintic; ignores
@@ -205,7 +217,7 @@ class CutlassNSInt8:
             return self._regular_i8(x, coeffs, eps, deterministic, "int8", block=True, out=out)
         if precision != "float8_e4m3fn":
             raise ValueError(f"Unsupported block-quantised precision: {precision}")
-        return self._run(native.ROUTE_BQ_FP8, x, coeffs, eps, native.F16, 128, precision, False, out)
+        return self._run(native.ROUTE_BQ_FP8, x, coeffs, eps, native.F16, 128, precision, False, out, deterministic)
 
 
 __all__ = ["CutlassNSInt8", "check_status", "status_word", "post_status", "raise_if_reported"]

@@ -15,7 +15,7 @@ from functools import lru_cache
 from .build import LIBRARY
 
 F32, F16, BF16 = 0, 1, 2
-ROUTE_FLOAT, ROUTE_GRAM, ROUTE_INT8, ROUTE_BQ_INT8, ROUTE_BQ_FP8, ROUTE_INT8_FACTORED = range(6)
+ROUTE_FLOAT, ROUTE_GRAM, ROUTE_INT8, ROUTE_BQ_INT8, ROUTE_BQ_FP8, ROUTE_INT8_FACTORED, ROUTE_INT8_CUBIC = range(7)
 
 
 class NativeError(RuntimeError):
@@ -35,6 +35,7 @@ _SIGNATURES = {
     "i8m_stats_scratch_bytes": (c_int, [c_int, c_longlong, POINTER(c_size_t)]),
     "i8m_stats": (c_int, [_P, c_int, c_int, c_longlong, _P, c_size_t, _P, _P, _P]),
     "i8m_stats_static": (c_int, [_P, c_int, c_int, c_longlong, _P, _P, _P]),
+    "i8m_stats_onepass": (c_int, [_P, c_int, c_int, c_longlong, _P, c_size_t, _P, _P, _P]),
     "i8m_normalize": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_float, _P]),
     "i8m_float_gemm": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
@@ -55,7 +56,7 @@ _SIGNATURES = {
     "i8m_ns_workspace_bytes": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                        POINTER(c_size_t)]),
     "i8m_ns_run": (c_int, [c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, POINTER(c_double),
-                           c_int, c_float, c_int, c_int, c_char_p, _P, c_size_t, _P, _P]),
+                           c_int, c_float, c_int, c_int, c_int, c_char_p, _P, c_size_t, _P, _P]),
     "i8m_momentum": (c_int, [POINTER(_P), POINTER(_P), c_int, _P, c_longlong, c_int, c_float,
                              c_float, c_int, _P]),
     "i8m_apply": (c_int, [POINTER(_P), c_int, _P, c_longlong, c_int, c_int, c_int, c_float,

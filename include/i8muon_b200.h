@@ -46,8 +46,12 @@ enum i8m_route {
   I8M_ROUTE_INT8 = 2,    /* _regular_i8    */
   I8M_ROUTE_BQ_INT8 = 3, /* _regular_bq, int8 blocks */
   I8M_ROUTE_BQ_FP8 = 4,  /* _regular_bq, E4M3 blocks */
-  I8M_ROUTE_INT8_FACTORED = 5 /* _regular_i8_factored: coefficient rows are (c, p, q) of
+  I8M_ROUTE_INT8_FACTORED = 5, /* _regular_i8_factored: coefficient rows are (c, p, q) of
                                  c * ((G + p I)^2 + q I), src/i8muon/_cutlass.py:93-128 */
+  I8M_ROUTE_INT8_CUBIC = 6    /* _regular_i8_grouped_cubic / _regular_i8_cubic_abc (src/i8muon/_cutlass_cubic.py:8-87):
+                                 row 0 is (input_gain, 0, 0), rows 1 .. steps-2 are (gain, diagonal shift, 0) of
+                                 T <- -gain (T T^T + shift I) T, the last row is the terminal quintic (a, b, c);
+                                 always all-INT8, fp16_first is ignored */
 };
 
 /* ---- library state ------------------------------------------------------ */
@@ -60,7 +64,10 @@ const char* i8m_last_error(void);
  * and GEMM counts once; memsets do not); used to report launches per step */
 unsigned long long i8m_launch_count(void);
 /* tests only: 1 replaces the TMA/tcgen05 mainloop by plain dot products inside
- * the epilogue threads (same epilogues); 0 restores the tensor-core path. */
+ * the epilogue threads (same epilogues); 2 keeps the tensor-core kernels of the block-quantised
+ * GEMMs but makes their producers issue no copy, so that every bounded device-side wait runs
+ * out (about two seconds), the status word receives a code and the kernel returns with nothing
+ * in flight; 0 restores the normal path.  Per calling thread. */
 int i8m_set_debug_core(int simt);
 /* Kernel variants a host-side tuner can choose between, the counterpart of the tile ids
  * that the reference's KernelFactory times (src/i8muon/_cuda_factory.py:62-102).
@@ -88,6 +95,12 @@ int i8m_set_variant(const char* operation, int variant);
 int i8m_stats_scratch_bytes(int batch, long long count, size_t* bytes);
 int i8m_stats(const void* x_device, int dtype, int batch, long long count, void* scratch_device,
               size_t scratch_bytes, float* norm_device, float* amax_device, i8m_stream_t stream);
+
+/* One-pass flavour (deterministic=False of the reference: fused sum of squares with atomics,
+ * src/i8muon/csrc/int8.cu:41-62): one launch; the floating-point summation order is not reproducible.
+ * scratch: 3 * batch 32-bit words of device memory (cleared by the call). */
+int i8m_stats_onepass(const void* x_device, int dtype, int batch, long long count, void* scratch_device,
+                      size_t scratch_bytes, float* norm_device, float* amax_device, i8m_stream_t stream);
 
 /* Same result as i8m_stats for callers that cannot allocate device memory.
  * No counterpart in the reference.  Some hosts of this library never get to call
@@ -171,9 +184,13 @@ int i8m_bq_gemm(int fp8, int mode, const void* a, const float* sa, const float* 
  *   compute      floating routes: I8M_F32 / I8M_F16 / I8M_BF16 (ignored otherwise)
  *   coeffs       steps rows of (a, b, c), host memory
  *   fp16_first   INT8 and BQ-INT8 routes: first row in FP16, rest quantised
+ *   deterministic  non-zero: two-pass statistics with a fixed summation order; zero: the one-pass
+ *                flavour with atomics (src/i8muon/_cutlass.py:189-194), one launch fewer, sum order free
  *   variants     kernel variants for this call: -1 = the calling thread's i8m_set_variant choices,
- *                otherwise (bq_gemm variant) | (wholek_gemm variant << 8); the thread's own
- *                choices are untouched
+ *                otherwise (bq_gemm variant) | (wholek_gemm variant << 8) | (its variant for the
+ *                polynomial product of the global-INT8 route << 16) | (for that route's update
+ *                product << 24), bits 8-15 then being the Gram product's; the thread's own choices
+ *                are untouched
  *   gram_order   GRAM route: restart string such as "00100" (NULL = default)
  *   workspace    device memory of at least i8m_ns_workspace_bytes(...) bytes,
  *                256-byte aligned; contents are scratch
@@ -182,7 +199,7 @@ int i8m_ns_workspace_bytes(int route, int batch, int rows, int cols, int dtype, 
                            int steps, int fp16_first, size_t* bytes);
 int i8m_ns_run(int route, const void* x_device, void* out_device, int dtype, int batch, int rows,
                int cols, int compute, const double* coeffs, int steps, float eps, int fp16_first,
-               int variants, const char* gram_order, void* workspace_device, size_t workspace_bytes,
+               int deterministic, int variants, const char* gram_order, void* workspace_device, size_t workspace_bytes,
                uint32_t* status_device, i8m_stream_t stream);
 
 /* ---- optimizer step kernels ------------------------------------------------

@@ -341,3 +341,39 @@ def test_grouped_cubic_and_cubic_abc(cuda_device):
         engine._regular_i8_cubic_abc(x.to(cuda_device), [(1.0, 1.0, 0.0), abc])     # b must be negative
     with pytest.raises(ValueError):
         CutlassNSInt8(autotune=True)._regular_i8_grouped_cubic(x.to(cuda_device), 1.0, [1.5], abc)
+
+
+def test_one_pass_statistics_and_nondeterministic_entry_points(cuda_device):
+    """``deterministic=False``: one-pass statistics with atomics (the reference's fused path,
+    src/i8muon/_cutlass.py:189-194).  The maximum is exact, the norm equal up to summation order, and the
+    entry points stay within their tolerance of the deterministic call."""
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn((3, 300, 520), generator=g) * 0.02).to(cuda_device)
+    scratch = torch.empty(3 * 3 * 4, dtype=torch.uint8, device=cuda_device)
+    norm, amax = torch.empty(3, device=cuda_device), torch.empty(3, device=cuda_device)
+    for _ in range(2):       # twice: the call clears its own scratch
+        native.call("i8m_stats_onepass", x.data_ptr(), native.F32, 3, 300 * 520, scratch.data_ptr(), scratch.numel(),
+                    norm.data_ptr(), amax.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert torch.equal(amax, x.abs().amax(dim=(1, 2)))
+        assert torch.allclose(norm, x.norm(dim=(1, 2)), rtol=2e-6, atol=0)
+    engine = CutlassNSInt8(fp16_first=False)
+    for fn, precision, tol in ((engine._regular_i8, "int8", 5e-2), (engine._regular_prec, "float32", 1e-5),
+                               (engine._regular_bq, "int8_bq", 5e-2)):
+        a = fn(x, C5, 1e-7, True, precision)
+        b = fn(x, C5, 1e-7, False, precision)
+        check_status()
+        assert rel(b, a) <= tol        # a norm that differs in the last bit moves a quantised route by ~1e-2
+
+
+def test_tile_overrides_select_kernels_of_the_same_arithmetic(cuda_device):
+    """``tiles=`` picks, per product of the global-INT8 route, between the persistent TMA kernel (the
+    reference's tile id 4) and the one-CTA-per-tile kernel (ids 0-3): results are bit-identical."""
+    g = torch.Generator().manual_seed(6)
+    x = (torch.randn((2, 272, 400), generator=g) * 1e-3).to(cuda_device)
+    want = CutlassNSInt8()._regular_i8(x, C5, 1e-7, True, "int8")
+    for tiles in ({"aat": 0}, {"square": 2, "update": 3}, {"aat": 4, "square": 4, "update": 4}, {"aat": 1, "square": 1, "update": 0}):
+        got = CutlassNSInt8(tiles=tiles)._regular_i8(x, C5, 1e-7, True, "int8")
+        check_status()
+        assert torch.equal(got, want), tiles
+    with pytest.raises(ValueError, match="tiles accepts"):
+        CutlassNSInt8(tiles={"aat": 7})

@@ -269,3 +269,34 @@ def test_float_gemm_modes(cuda_device, core, dtype, tol):
             want = want.mT if tr else want
             step = max(tol, {torch.float32: 0, torch.float16: 2 ** -10, torch.bfloat16: 2 ** -7}[out_dtype])
             assert bool(((fin.double() - want).abs() <= 2 * step * want.abs() + 1e-6).all())
+
+
+# ------------------------------------------------------------------ bounded waits
+@pytest.mark.parametrize("variant", [0, 1], ids=["split-tail", "fused-tail"])
+def test_bounded_waits_run_out_and_report_when_the_producer_issues_nothing(cuda_device, variant):
+    """The failure path of the block-quantised GEMM kernels, made on purpose in the one way that leaves nothing in
+    flight: a host-set flag lets the producers return without issuing a copy (one tile, one CTA).  The issuers'
+    wait for operands runs out after its two-second limit, sets the abort flag, the fold and tail warps leave at
+    their next poll, tensor memory is freed, and the status word holds a timeout code.  The same launch without
+    the flag is then correct, on the same context."""
+    dev = cuda_device
+    x = make_input((1, 128, 256), torch.bfloat16, 8).to(dev)
+    norm, _ = H.stats(x)
+    a, at, sa = H.bq_quant(x, norm, False)
+    native.call("i8m_set_variant", b"bq_gemm", variant)
+    try:
+        want = H.bq_gemm(False, 0, a, sa, a, sa, lm=128, ln=128)
+        assert H.status_ok(dev) == 0
+        native.call("i8m_set_debug_core", 2)
+        H.bq_gemm(False, 0, a, sa, a, sa, lm=128, ln=128)
+        code = H.status_ok(dev)            # synchronises: about two seconds
+        assert code & 0xf00 in (0x100, 0x200, 0x300, 0x400) and code != 0
+        native.call("i8m_set_debug_core", 0)
+        again = H.bq_gemm(False, 0, a, sa, a, sa, lm=128, ln=128)
+        assert H.status_ok(dev) == 0
+        for p, q in zip(want, again):
+            if isinstance(p, torch.Tensor):
+                assert torch.equal(p, q)
+    finally:
+        native.call("i8m_set_debug_core", 0)
+        native.call("i8m_set_variant", b"bq_gemm", 0)
