@@ -29,7 +29,9 @@
 
 namespace i8m {
 
-enum BqMode : int { BQ_GRAM = 0, BQ_POLY = 1, BQ_UPDATE = 2, BQ_UPDATE_FINAL = 3 };
+// BQ_PLAIN: the tail alone on values that another GEMM's epilogue computed (the FP16 first row of an
+// fp16-first call): tile maximum, quantise, store A, A^T and the block scale as BQ_UPDATE does.
+enum BqMode : int { BQ_GRAM = 0, BQ_POLY = 1, BQ_UPDATE = 2, BQ_UPDATE_FINAL = 3, BQ_PLAIN = 4 };
 
 struct BqArgs {
   const float* sa;        // scales of the left operand  (batch, m/128, k/128)
@@ -99,7 +101,7 @@ struct EpiBq {
   static constexpr int PROMOTE_KB = 1;
   static constexpr int NBUF = 4;           // TMEM accumulators of 128 columns
   static constexpr bool PRESET = !FP8;     // INT8: accumulators start at the bias constant
-  static constexpr bool SPLIT_TAIL = MODE != BQ_UPDATE_FINAL;   // has a split_tail() for bq_split_kernel
+  static constexpr bool SPLIT_TAIL = MODE != BQ_UPDATE_FINAL && MODE != BQ_PLAIN;   // has a split_tail()
   static constexpr int STAGES = 4;
   static constexpr int MIN_CTAS = 1;
   // eight epilogue warps: two per scheduler, each thread owns half a row (64 columns),
@@ -188,7 +190,7 @@ struct EpiBq {
     Pre p;
     p.drow = 0.f; p.stile = 0.f;
     const int colbase = t.col0 + t.half * CPT;
-    if constexpr (MODE != BQ_GRAM) p.drow = a.da[size_t(t.b) * g.m + t.row];
+    if constexpr (MODE != BQ_GRAM && MODE != BQ_PLAIN) p.drow = a.da[size_t(t.b) * g.m + t.row];
     if constexpr (MODE == BQ_POLY) p.stile = a.sa[(size_t(t.b) * mq + t.tm) * kq + t.tn];
     if constexpr (MODE == BQ_UPDATE || MODE == BQ_UPDATE_FINAL)
       p.stile = a.sb[(size_t(t.b) * kq + t.tm) * nq + t.tn];
@@ -418,6 +420,7 @@ struct EpiBq {
     const bool in_rows = t.row < g.lm;
     // thread-uniform shortcuts: most threads own no padding and no diagonal element
     const bool inside = in_rows && colbase + CPT <= g.ln;
+    constexpr bool RECT = MODE == BQ_UPDATE || MODE == BQ_PLAIN;   // rectangular result with a transposed copy
     const bool has_diag = (MODE == BQ_GRAM || MODE == BQ_POLY) && t.tm == t.tn;
     const float drow = pre.drow, stile = pre.stile;
     if constexpr (MODE == BQ_POLY) {
@@ -430,7 +433,7 @@ struct EpiBq {
 #pragma unroll
     for (int c16 = 0; c16 < CPT / 16; ++c16) {
       uint32_t words[4] = {0u, 0u, 0u, 0u};
-      if constexpr (MODE != BQ_GRAM) {
+      if constexpr (MODE != BQ_GRAM && MODE != BQ_PLAIN) {
         const uint4 w = pre.comp[c16];
         words[0] = w.x; words[1] = w.y; words[2] = w.z; words[3] = w.w;
       }
@@ -439,7 +442,9 @@ struct EpiBq {
         const int j = c16 * 16 + jj;
         const int col = colbase + j;
         float val = vals[j];
-        if constexpr (MODE == BQ_GRAM) {
+        if constexpr (MODE == BQ_PLAIN) {
+          // nothing to add: the caller's values are the result
+        } else if constexpr (MODE == BQ_GRAM) {
           if (has_diag && col == t.row) {
             if (live) a.dout[size_t(t.b) * g.m + t.row] = in_rows ? val : 0.f;
             val = 0.f;
@@ -519,14 +524,14 @@ struct EpiBq {
       const float scale = 1.f / multiplier;
       if (store && t.r == 0 && t.half == 0) {
         a.so[(size_t(t.b) * mq + t.tm) * nq + t.tn] = scale;
-        if constexpr (MODE != BQ_UPDATE) a.so[(size_t(t.b) * mq + t.tn) * nq + t.tm] = scale;
+        if constexpr (!RECT) a.so[(size_t(t.b) * mq + t.tn) * nq + t.tm] = scale;
       }
       uint8_t* out = static_cast<uint8_t*>(a.out);
-      const bool diag_tile = (MODE != BQ_UPDATE) && t.tm == t.tn;
+      const bool diag_tile = !RECT && t.tm == t.tn;
       // transposed target: A^T (update) or the mirrored tile (gram / poly)
-      uint8_t* tdst = (MODE == BQ_UPDATE) ? static_cast<uint8_t*>(a.out_t) : out;
-      const int trows = (MODE == BQ_UPDATE) ? g.n : g.m;
-      const int tld = (MODE == BQ_UPDATE) ? g.m : g.n;
+      uint8_t* tdst = RECT ? static_cast<uint8_t*>(a.out_t) : out;
+      const int trows = RECT ? g.n : g.m;
+      const int tld = RECT ? g.m : g.n;
       uint4* dst = reinterpret_cast<uint4*>(out + (size_t(t.b) * g.m + t.row) * g.n + colbase);
       // With a staging tile in shared memory the transposed copy is written there byte by
       // byte (conflict free: a warp's lanes are consecutive rows) and then leaves as

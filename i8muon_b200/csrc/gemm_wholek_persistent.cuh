@@ -22,6 +22,7 @@
 // shared-memory bandwidth, and a third of the time per tile was fill, drain and epilogue.
 #pragma once
 #include "gemm_core.cuh"
+#include <type_traits>
 
 namespace i8m {
 
@@ -30,6 +31,12 @@ constexpr int WKP_THREADS = 384;
 constexpr int WKP_NBUF = 4;      // two streams x two accumulators
 constexpr int WKP_CTRL_REGS = 56;
 constexpr int WKP_EPI_REGS = 224;
+
+// Epilogues with a tile-wide tail (a maximum over the tile, a staged transposed store) declare TILE_SYNC.
+template <class Epi, class = void>
+struct WholekTileSync { static constexpr bool value = false; };
+template <class Epi>
+struct WholekTileSync<Epi, std::enable_if_t<Epi::TILE_SYNC>> { static constexpr bool value = true; };
 
 template <class Epi>
 __global__ void __launch_bounds__(WKP_THREADS, 1)
@@ -46,6 +53,7 @@ wholek_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* tsm = reinterpret_cast<uint8_t*>(ctrl + 1);   // staging tile of epilogues that have a tile tail
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -160,7 +168,7 @@ wholek_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     t.ew = warp - 4; t.half = (warp - 4) >> 2;
     t.r = t.q * 32 + lane;
     t.ctrl = ctrl;
-    t.red = ctrl->red; t.diag = ctrl->diag; t.tsm = nullptr;
+    t.red = ctrl->red; t.diag = ctrl->diag; t.tsm = WholekTileSync<Epi>::value ? tsm : nullptr;
     t.c_begin = t.half * 2; t.c_end = t.half * 2 + 2;
     bool ok = true;
     for (int it = 0; it < my_tiles; ++it) {
@@ -169,11 +177,25 @@ wholek_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       t.row = t.row0 + t.r;
       const int buf = 2 * (it & 1) + ((it >> 1) & 1);   // stream it & 1, its tile number it >> 1
       if (ok) ok = mbar_wait_warp(accf0 + 8u * uint32_t(buf), uint32_t(it >> 2) & 1u, abort_flag);
-      if (!ok) continue;  // a warp that gave up skips the remaining tiles; the status word says so
-      tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16) + uint32_t(buf * TILE);
       AccWholeK<Epi::KIND, typename Epi::Elem, false> acc{g, t, taddr};
+      if constexpr (WholekTileSync<Epi>::value) {
+        // this epilogue's tile tail meets on named barriers: a warp that gave up walks through them
+        // too (without loading or storing), so the others can never wait for it
+        t.red = ctrl->red2[it & 1];
+        if (ok) tc_fence_after();
+        Epi::run_sync(g, args, t, acc, ok);
+        if (ok) {
+          tc_fence_before();
+          __syncwarp();
+          mbar_arrive_if(acce0 + 8u * uint32_t(buf), lane == 0 ? 1u : 0u);
+        }
+        continue;
+      } else {
+      if (!ok) continue;  // a warp that gave up skips the remaining tiles; the status word says so
+      tc_fence_after();
       Epi::run(g, args, t, acc);
+      }
       tc_fence_before();
       __syncwarp();
       mbar_arrive_if(acce0 + 8u * uint32_t(buf), lane == 0 ? 1u : 0u);

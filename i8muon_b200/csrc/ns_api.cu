@@ -5,6 +5,7 @@
 #include "../../include/i8muon_b200.h"
 #include "epi_bq.cuh"
 #include "epi_float.cuh"
+#include "epi_float_bq.cuh"
 #include "epi_int8.cuh"
 #include "gemm_bq_persistent.cuh"
 #include "gemm_bq_split.cuh"
@@ -448,6 +449,53 @@ extern "C" int i8m_float_gemm(const void* left, const void* left_lo, const void*
   return fail(I8M_E_ARGUMENT, "float_gemm: bad compute dtype %d", compute);
 }
 
+// FP16 / BF16 product whose result leaves as block-quantised INT8 operands (the end of the FP16 first
+// iteration of an fp16-first INT8-BQ call): persistent kernel only.
+template <typename E>
+static int float_gemm_to_bq_typed(const void* left, const void* right_t, const FloatToBqArgs& args, int batch, int m,
+                                  int n, int k, int lm, int ln, unsigned* status, cudaStream_t stream) {
+  using Epi = EpiFloatToBq<E>;
+  GemmGeom g;
+  g.batch = batch; g.m = m; g.n = n; g.k = k; g.lm = lm; g.ln = ln;
+  g.tiles_m = cdiv(m, TILE); g.tiles_n = cdiv(n, TILE);
+  g.sym = 0;
+  g.tiles_per_batch = g.tiles_m * g.tiles_n;
+  g.num_kb = cdiv((long long)k * 2, 128);
+  g.debug_simt = 0;
+  g.a_raw = left; g.b_raw = right_t; g.status = status;
+  const long long blocks = (long long)g.tiles_per_batch * batch;
+  if (blocks > 0x7fffffffLL) return fail(I8M_E_LIMIT, "float_gemm_to_bq: too many tiles");
+  CUtensorMap ma, mb;
+  if (int rc = make_operand_map(&ma, left, 2, k, m, batch)) return rc;
+  if (int rc = make_operand_map(&mb, right_t, 2, k, n, batch)) return rc;
+  constexpr size_t SMEM = size_t(WKP_STAGES) * 2 * TILE_BYTES + sizeof(Ctrl) + Epi::TSM_BYTES + 1024;
+  auto kernel = wholek_persistent_kernel<Epi>;
+  CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
+  const unsigned grid = unsigned(std::min<long long>(blocks, sm_count()));
+  kernel<<<grid, WKP_THREADS, SMEM, stream>>>(ma, mb, g, args);
+  LAUNCH_CHECK("float_gemm_to_bq");
+  return 0;
+}
+
+extern "C" int i8m_float_gemm_to_bq(const void* left, const void* right_t, void* q, void* q_t, float* scale,
+                                    int compute, int user_dtype, int batch, int m, int n, int k, int lm, int ln,
+                                    int lp, int hp, uint32_t* status, i8m_stream_t stream) {
+  if (!left || !right_t || !q || !q_t || !scale || !status) return fail(I8M_E_ARGUMENT, "float_gemm_to_bq: null pointer");
+  if (batch < 1 || m < 1 || n < 1 || k < 1 || lm < 1 || ln < 1 || lm > m || ln > n)
+    return fail(I8M_E_ARGUMENT, "float_gemm_to_bq: bad extents");
+  if (lp % 128 || hp % 128 || lp < m || hp < n || cdiv(lp, 128) != cdiv(m, 128) || cdiv(hp, 128) != cdiv(n, 128))
+    return fail(I8M_E_ARGUMENT, "float_gemm_to_bq: lp, hp must be m, n rounded up to multiples of 128");
+  if (!float_dtype_ok(user_dtype)) return fail(I8M_E_ARGUMENT, "float_gemm_to_bq: bad user dtype");
+  FloatToBqArgs a;
+  a.q = static_cast<uint8_t*>(q); a.qt = static_cast<uint8_t*>(q_t); a.scale = scale;
+  a.lp = lp; a.hp = hp; a.user_dtype = user_dtype;
+  if (compute == I8M_F16)
+    return float_gemm_to_bq_typed<__half>(left, right_t, a, batch, m, n, k, lm, ln, status, S(stream));
+  if (compute == I8M_BF16)
+    return float_gemm_to_bq_typed<__nv_bfloat16>(left, right_t, a, batch, m, n, k, lm, ln, status, S(stream));
+  return fail(I8M_E_ARGUMENT, "float_gemm_to_bq: compute must be a 16-bit type");
+}
+
 // ====================================================== global INT8 path
 extern "C" int i8m_input_quant(const void* x, int in_dtype, const float* amax, const float* norm,
                                int8_t* a8, int8_t* a8_t, float* a_scale, int batch, int rows,
@@ -721,6 +769,7 @@ struct NsCall {
   int route, dtype, batch, rows, cols, compute, steps, fp16_first;
   int factored = 0;   // coefficient rows are (c, p, q) of c * ((G + p I)^2 + q I)
   int deterministic = 1;   // 0: one-pass statistics with atomics (summation order not reproducible)
+  int fuse_first_row = 1;   // fp16-first INT8-BQ: the first row's update quantises its own result
   int wholek[3] = {-1, -1, -1};   // global INT8: kernel variant of the Gram / square / update product (-1: thread's)
   const void* x;
   void* out;
@@ -755,9 +804,16 @@ FMat take_fmat(Bump& ws, size_t elems, int compute) {
 }
 
 // floating NS (regular and Gram); with plan == true only the workspace is sized.
+struct BqOperands {   // where a floating first row leaves its result for the block-quantised rows
+  uint8_t* a = nullptr;
+  uint8_t* at = nullptr;
+  float* sa = nullptr;
+  int lp = 0, hp = 0;
+};
+
 int run_float(const NsCall& c, Bump& ws, bool plan, bool gram, const void* x, void* out,
               int out_dtype, int steps, const double* coeffs, int compute, bool normalize_input,
-              bool factored = false) {
+              bool factored = false, const BqOperands* to_bq = nullptr) {
   const int B = c.batch, rows = c.rows, cols = c.cols;
   const int l = std::min(rows, cols), h = std::max(rows, cols);
   const int lp = pad_to(l, 16), hp = pad_to(h, 16);
@@ -805,6 +861,13 @@ int run_float(const NsCall& c, Bump& ws, bool plan, bool gram, const void* x, vo
       }
       if (int rc = gemm(r, r, q0, none, 1, lp, lp, l, 1, 0, 0, nullptr, ca, cb, cc)) return rc;
       const bool final = it == steps - 1;
+      if (final && to_bq) {
+        // the result stays in the wide orientation and leaves as INT8 blocks (no transposition back)
+        if (int rc = i8m_float_gemm_to_bq(q0.p, at.p, to_bq->a, to_bq->at, to_bq->sa, compute, out_dtype, B, lp, hp, lp,
+                                          l, h, to_bq->lp, to_bq->hp, c.status, c.stream))
+          return rc;
+        return 0;
+      }
       if (int rc = gemm(q0, at, y, yt, 0, hp, lp, h, 0, final, final && transpose, out, 0, 0, 0)) return rc;
       if (!final) { std::swap(a, y); std::swap(at, yt); }
     }
@@ -983,20 +1046,21 @@ int run_int8_cubic(const NsCall& c, Bump& ws, bool plan) {
 
 // block-quantised NS (src/i8muon/_cutlass_bq.py:15-70)
 int run_bq(const NsCall& c, Bump& ws, bool plan, bool fp8, const void* x, int steps,
-           const double* coeffs, bool normalize_input) {
+           const double* coeffs, bool normalize_input, const BqOperands* given = nullptr) {
   const int B = c.batch, rows = c.rows, cols = c.cols;
   const int l = std::min(rows, cols), h = std::max(rows, cols);
   const int lp = pad_to(l, 128), hp = pad_to(h, 128);
   const int transpose = rows > cols;
   const size_t wide = size_t(B) * lp * hp, sq = size_t(B) * lp * lp;
   const int lq = lp / 128, hq = hp / 128;
-  uint8_t* a = ws.take_n<uint8_t>(wide);
-  uint8_t* at = ws.take_n<uint8_t>(wide);
+  // `given`: the operands were quantised already (by the floating first row's epilogue)
+  uint8_t* a = given ? given->a : ws.take_n<uint8_t>(wide);
+  uint8_t* at = given ? given->at : ws.take_n<uint8_t>(wide);
   uint8_t* y = ws.take_n<uint8_t>(wide);
   uint8_t* yt = ws.take_n<uint8_t>(wide);
   uint8_t* gq = ws.take_n<uint8_t>(sq);
   uint8_t* pq = ws.take_n<uint8_t>(sq);
-  float* sa = ws.take_n<float>(size_t(B) * lq * hq);
+  float* sa = given ? given->sa : ws.take_n<float>(size_t(B) * lq * hq);
   float* sy = ws.take_n<float>(size_t(B) * lq * hq);
   float* sg = ws.take_n<float>(size_t(B) * lq * lq);
   float* sp = ws.take_n<float>(size_t(B) * lq * lq);
@@ -1007,11 +1071,13 @@ int run_bq(const NsCall& c, Bump& ws, bool plan, bool fp8, const void* x, int st
   void* scratch = ws.take(sbytes);
   if (plan) return 0;
 
-  if (normalize_input)
-    if (int rc = call_stats(c, x, B, (long long)rows * cols, scratch, sbytes, norm, nullptr)) return rc;
-  if (int rc = i8m_bq_quant(x, c.dtype, normalize_input ? norm : nullptr, a, at, sa, fp8, B, rows, cols,
-                            lp, hp, transpose, c.eps, c.stream))
-    return rc;
+  if (!given) {
+    if (normalize_input)
+      if (int rc = call_stats(c, x, B, (long long)rows * cols, scratch, sbytes, norm, nullptr)) return rc;
+    if (int rc = i8m_bq_quant(x, c.dtype, normalize_input ? norm : nullptr, a, at, sa, fp8, B, rows, cols,
+                              lp, hp, transpose, c.eps, c.stream))
+      return rc;
+  }
   for (int it = 0; it < steps; ++it) {
     const float ca = float(coeffs[3 * it]), cb = float(coeffs[3 * it + 1]), cc = float(coeffs[3 * it + 2]);
     if (int rc = i8m_bq_gemm(fp8, 0, a, sa, nullptr, a, sa, nullptr, gq, nullptr, sg, dg, B, lp, lp, hp, l,
@@ -1065,6 +1131,24 @@ int ns_dispatch(const NsCall& c, Bump& ws, bool plan) {
       // quantised rows without re-normalising (src/i8muon/_cutlass.py:137-142).
       if (c.steps == 1)
         return run_float(c, ws, plan, false, c.x, c.out, c.dtype, 1, c.coeffs, I8M_F16, true);
+      if (bq && c.fuse_first_row) {
+        // The first row's update product quantises its own result (the CTA tile is the quantisation
+        // block): no 16-bit intermediate in HBM, no standalone quantisation pass.
+        const int l = std::min(c.rows, c.cols), h = std::max(c.rows, c.cols);
+        BqOperands ops;
+        ops.lp = pad_to(l, 128); ops.hp = pad_to(h, 128);
+        const size_t wide = size_t(c.batch) * ops.lp * ops.hp;
+        ops.a = ws.take_n<uint8_t>(wide);
+        ops.at = ws.take_n<uint8_t>(wide);
+        ops.sa = ws.take_n<float>(size_t(c.batch) * (ops.lp / 128) * (ops.hp / 128));
+        const size_t mark = ws.used;
+        if (int rc = run_float(c, ws, plan, false, c.x, nullptr, c.dtype, 1, c.coeffs, I8M_F16, true, false, &ops)) return rc;
+        const size_t after_float = ws.used;
+        ws.used = mark;  // the quantised rows reuse the floating stage's scratch
+        const int rc = run_bq(c, ws, plan, false, nullptr, c.steps - 1, plan ? nullptr : c.coeffs + 3, false, &ops);
+        ws.used = std::max(ws.used, after_float);
+        return rc;
+      }
       void* first = ws.take(size_t(c.batch) * c.rows * c.cols * dtype_size(c.dtype));
       size_t mark = ws.used;
       if (int rc = run_float(c, ws, plan, false, c.x, first, c.dtype, 1, c.coeffs, I8M_F16, true)) return rc;

@@ -41,6 +41,8 @@ _SIGNATURES = {
     "i8m_float_gemm": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
                                c_float, _P, _P]),
+    "i8m_float_gemm_to_bq": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_int, _P, _P]),
     "i8m_input_quant": (c_int, [_P, c_int, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int,
                                 c_int, c_float, _P]),
     "i8m_i8_gemm": (c_int, [c_int, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int,

@@ -139,6 +139,16 @@ int i8m_float_gemm(const void* left, const void* left_lo, const void* right_t,
                    int symmetric, int final, int transpose, int out_dtype, float ca, float cb,
                    float cc, uint32_t* status_device, i8m_stream_t stream);
 
+/* The update product of an FP16 / BF16 iteration whose result leaves as 128 x 128 block-quantised INT8
+ * operands: out = left * right_t^T is rounded to `compute`, then to `user_dtype` (what the floating route
+ * stores, src/i8muon/csrc/prec.cu:159-164), and each 128 x 128 CTA tile takes its maximum, scale and codes as
+ * quant does with inv = 1 (src/i8muon/csrc/bq.cu:41-101): q (batch, lp, hp), q_t (batch, hp, lp), scale
+ * (batch, lp/128, hp/128), lp / hp = m / n rounded up to 128.  Replaces, for the fp16-first INT8-BQ call,
+ * the final store of gemm (prec.cu) plus quant (bq.cu) of src/i8muon/_cutlass.py:137-142. */
+int i8m_float_gemm_to_bq(const void* left, const void* right_t, void* q, void* q_t, float* scale, int compute,
+                         int user_dtype, int batch, int m, int n, int k, int lm, int ln, int lp, int hp,
+                         uint32_t* status_device, i8m_stream_t stream);
+
 /* ---- stage level: global-scale INT8 path --------------------------------- */
 /* input_quant: src/i8muon/csrc/int8.cu:508-527 (norm_device NULL = no normalisation) */
 int i8m_input_quant(const void* x_device, int in_dtype, const float* amax_device,

@@ -300,3 +300,30 @@ def test_bounded_waits_run_out_and_report_when_the_producer_issues_nothing(cuda_
     finally:
         native.call("i8m_set_debug_core", 0)
         native.call("i8m_set_variant", b"bq_gemm", 0)
+
+
+# ------------------------------------------------------------------ fused first row of an fp16-first call
+@pytest.mark.parametrize("b,l,h", [(2, 144, 400), (1, 200, 330), (1, 1536, 2048)])
+@pytest.mark.parametrize("user", [torch.bfloat16, torch.float16, torch.float32])
+def test_float_update_that_quantises_its_own_result_matches_the_two_kernel_sequence(cuda_device, b, l, h, user):
+    """``i8m_float_gemm_to_bq`` (the FP16 first row's update product whose epilogue is the block quantiser)
+    against the sequence it replaces: the floating route's final store in the caller's dtype followed by the
+    standalone quantisation pass without normalisation.  Codes, transposed codes and scales are bit-identical."""
+    dev = cuda_device
+    g = torch.Generator().manual_seed(12)
+    lp16, hp16 = -(-l // 16) * 16, -(-h // 16) * 16
+    lp, hp = -(-l // 128) * 128, -(-h // 128) * 128
+    q0 = torch.zeros((b, lp16, lp16), dtype=torch.float16)
+    q0[:, :l, :l] = (torch.randn((b, l, l), generator=g) * 0.05).half()
+    at = torch.zeros((b, hp16, lp16), dtype=torch.float16)
+    at[:, :h, :l] = (torch.randn((b, h, l), generator=g) * 0.05).half()
+    q0, at = q0.to(dev), at.to(dev)
+    first, *_ = H.float_gemm(q0, at, final=True, transpose=False, out_dtype=user, lm=l, ln=h)   # (b, l, h)
+    want_a, want_at, want_sa = H.bq_quant(first, None, False)
+    a = torch.full((b, lp, hp), 77, device=dev, dtype=torch.uint8)
+    a_t = torch.full((b, hp, lp), 77, device=dev, dtype=torch.uint8)
+    sa = torch.empty((b, lp // 128, hp // 128), device=dev)
+    native.call("i8m_float_gemm_to_bq", q0.data_ptr(), at.data_ptr(), a.data_ptr(), a_t.data_ptr(), sa.data_ptr(),
+                native.F16, H.DT[user], b, lp16, hp16, lp16, l, h, lp, hp, H.status_word(dev).data_ptr(), H._stream())
+    assert H.status_ok(dev) == 0
+    assert torch.equal(a, want_a) and torch.equal(a_t, want_at) and torch.equal(sa, want_sa)
