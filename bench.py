@@ -262,7 +262,7 @@ def other_config(name):
     bf16, f32 = torch.bfloat16, torch.float32
     if name == "cfg1":
         return dict(shapes=[(1024, 4096)], pdtype=f32, gdtype=f32, pstd=1.0, gstd=1.0, steps=5, method="int8_safe",
-                    muon=dict(precision="float32", use_gram=False), graph=False, peak="tf32x3",
+                    muon=dict(precision="float32", use_gram=False), graph=True, peak="tf32x3",
                     what="FP32 regular NS (3 x TF32 products), one 1024x4096 matrix, int8_safe x5")
     if name == "cfg2":
         return dict(shapes=[(768, 3072)] * 48, pdtype=bf16, gdtype=bf16, pstd=0.02, gstd=0.02, steps=5,
@@ -313,7 +313,12 @@ def run_other_config(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        if args.reserve_sms > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(args.reserve_sms))
         dist.init_process_group("nccl", device_id=dev)
+        if args.reserve_sms > 0:
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            native.call("i8m_set_cta_limit", sms - args.reserve_sms)
     gen = torch.Generator(device=dev).manual_seed(1000)
     coeffs = recommend_coefficients(cfg["steps"], method=cfg["method"])
 
@@ -366,9 +371,9 @@ def run_other_config(args):
     else:
         engine = CutlassNSInt8(fp16_first=bool(muon_kw.pop("fp16_first", True)))
         ops = native_step_ops(engine, ns_coefficients=coeffs, **{k: v for k, v in muon_kw.items()})
-        stepper = ShardedMuonStep([p.data for p in params], cfg["steps"], ops)
-        buffers = {i: torch.zeros_like(grads[i]) for i in stepper.plan.owned(rank)}
         plain = [p.data for p in params]
+        stepper = ShardedMuonStep(plain, cfg["steps"], ops, adopt_parameters=bool(args.adopt))
+        buffers = {i: torch.zeros_like(grads[i]) for i in stepper.plan.owned(rank)}
         host = [torch.empty(g.shape, dtype=g.dtype).pin_memory().copy_(g) for g in grads]
 
         def step():
@@ -522,7 +527,8 @@ def run_native(args):
     if world > 1:
         # The persistent GEMM kernels own every SM they run on, so the all-gather (an SM kernel) gets
         # SMs of its own: the GEMMs launch on all but `--reserve-sms` SMs and NCCL is held to as many CTAs.
-        os.environ.setdefault("NCCL_MAX_CTAS", str(max(1, args.reserve_sms)))
+        if args.reserve_sms > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(args.reserve_sms))
         dist.init_process_group("nccl", device_id=dev)
         if args.reserve_sms > 0:
             sms = torch.cuda.get_device_properties(dev).multi_processor_count

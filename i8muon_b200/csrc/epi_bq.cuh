@@ -101,7 +101,7 @@ struct EpiBq {
   static constexpr int PROMOTE_KB = 1;
   static constexpr int NBUF = 4;           // TMEM accumulators of 128 columns
   static constexpr bool PRESET = !FP8;     // INT8: accumulators start at the bias constant
-  static constexpr bool SPLIT_TAIL = MODE != BQ_UPDATE_FINAL && MODE != BQ_PLAIN;   // has a split_tail()
+  static constexpr bool SPLIT_TAIL = MODE != BQ_PLAIN;   // has a split_tail() for bq_split_kernel
   static constexpr int STAGES = 4;
   static constexpr int MIN_CTAS = 1;
   // eight epilogue warps: two per scheduler, each thread owns half a row (64 columns),
@@ -306,11 +306,116 @@ struct EpiBq {
     return mx;
   }
 
+  // eight consecutive values -> the caller's 16-bit dtype, one 16-byte vector
+  static __device__ __forceinline__ uint4 pack8_16bit(const float* v, int dtype) {
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (dtype == DT_BF16)
+        w[e] = uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(v[2 * e]))) |
+               (uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(v[2 * e + 1]))) << 16);
+      else
+        w[e] = uint32_t(__half_as_ushort(__float2half_rn(v[2 * e]))) |
+               (uint32_t(__half_as_ushort(__float2half_rn(v[2 * e + 1]))) << 16);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+
+  // The last update of a call: value = fma(a * dP, sA, total) cast to the caller's dtype, un-padded, in the
+  // caller's orientation.  Row-major results leave straight from pass 0; a transposed result (rows > cols
+  // inputs) goes back into the parked tile and leaves column by column after the four warps have met.
+  static __device__ __forceinline__ bool split_tail_final(const GemmGeom& g, const Args& a, const int b, const int tm,
+                                                          const int tn, const int tid, const int it, const uint32_t park,
+                                                          Ctrl* ctrl, volatile uint32_t* abort_flag, const int nq,
+                                                          const int kq) {
+    const int lane = tid & 31;
+    const int row0 = tm * TILE, col0 = tn * TILE;
+    const int row = row0 + tid;
+    const bool in_rows = row < g.lm;
+    const float drow = a.da[size_t(b) * g.m + row];
+    const float stile = a.sb[(size_t(b) * kq + tm) * nq + tn];
+    const uint8_t* comp = a.row_b + (size_t(b) * g.m + row) * g.n + col0;
+    const uint32_t my_row = park + uint32_t(tid * PARK_PITCH) * 4u;
+    const int esz = a.out_dtype == DT_F32 ? 4 : 2;
+    const bool vec_rows = !a.transpose && in_rows && (g.ln % 8) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
+#pragma unroll 1
+    for (int j = 0; j < TILE / 16; ++j) {
+      const uint4 cw = *reinterpret_cast<const uint4*>(comp + 16 * j);
+      const uint32_t words[4] = {cw.x, cw.y, cw.z, cw.w};
+      float vals[16];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float4 x = lds128(my_row + uint32_t(16 * j + 4 * q4) * 4u);
+        vals[4 * q4] = x.x; vals[4 * q4 + 1] = x.y; vals[4 * q4 + 2] = x.z; vals[4 * q4 + 3] = x.w;
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e)
+        vals[e] = __fmaf_rn(__fmul_rn(code_to_float(words[e >> 2], e & 3), drow), stile, vals[e]);
+      if (a.transpose) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          sts128(my_row + uint32_t(16 * j + 4 * q4) * 4u,
+                 make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]));
+      } else if (in_rows) {
+        const int col = col0 + 16 * j;
+        const size_t idx = (size_t(b) * g.lm + row) * g.ln + col;
+        if (vec_rows && col + 16 <= g.ln) {
+          if (esz == 2) {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + idx);
+            dst[0] = pack8_16bit(vals, a.out_dtype);
+            dst[1] = pack8_16bit(vals + 8, a.out_dtype);
+          } else {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(a.out) + idx);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+              dst[q4] = make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            if (col + e < g.ln) store_user(a.out, a.out_dtype, idx + e, vals[e]);
+        }
+      }
+    }
+    if (!a.transpose) return true;
+    // transposed result: the warps meet (rows of other warps are read below), then thread = tile column
+    __syncwarp();
+    const uint32_t meet = smem_u32(&ctrl->tail_sync);
+    mbar_arrive_if(meet, lane == 0 ? 1u : 0u);
+    if (!mbar_wait_warp_inline(meet, uint32_t(it) & 1u, abort_flag)) return false;
+    const int col = col0 + tid;
+    if (col >= g.ln) return true;
+    const uint32_t my_col = park + uint32_t(tid) * 4u;
+    const size_t tbase = (size_t(b) * g.ln + col) * g.lm + row0;      // out is (batch, ln, lm)
+    const bool vec_cols = (g.lm % 8) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
+#pragma unroll 1
+    for (int j = 0; j < TILE / 8; ++j) {
+      if (row0 + 8 * j >= g.lm) break;
+      float vals[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) vals[e] = lds32(my_col + uint32_t((8 * j + e) * PARK_PITCH) * 4u);
+      if (vec_cols && row0 + 8 * j + 8 <= g.lm) {
+        if (esz == 2) {
+          *reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.out) + tbase + 8 * j) = pack8_16bit(vals, a.out_dtype);
+        } else {
+          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(a.out) + tbase + 8 * j);
+          dst[0] = make_float4(vals[0], vals[1], vals[2], vals[3]);
+          dst[1] = make_float4(vals[4], vals[5], vals[6], vals[7]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (row0 + 8 * j + e < g.lm) store_user(a.out, a.out_dtype, tbase + 8 * j + e, vals[e]);
+      }
+    }
+    return true;
+  }
+
   static __device__ __forceinline__ bool split_tail(const GemmGeom& g, const Args& a, const int b, const int tm,
                                                     const int tn, const int tid, const int it, const uint32_t park,
                                                     Ctrl* ctrl, volatile uint32_t* abort_flag, const int mq,
                                                     const int nq, const int kq) {
-    static_assert(MODE != BQ_UPDATE_FINAL, "the final update keeps the fused tail");
+    if constexpr (MODE == BQ_UPDATE_FINAL) return split_tail_final(g, a, b, tm, tn, tid, it, park, ctrl, abort_flag, nq, kq);
     const int lane = tid & 31, w = tid >> 5;
     const int row0 = tm * TILE, col0 = tn * TILE;
     const int row = row0 + tid;

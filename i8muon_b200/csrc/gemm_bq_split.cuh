@@ -14,8 +14,8 @@
 // Shared memory: a four-stage operand ring (128 KB), the parked tile (66 KB), the scale ring.
 // Hand-over: park_full (8 fold-warp arrivals) / park_empty (4 tail-warp arrivals), both mbarriers
 // with bounded waits; a role that gives up sets the abort flag and every other role leaves at its
-// next poll.  The final update (cast to the caller's dtype, no quantisation) stays with
-// bq_persistent_kernel.
+// next poll.  The final update (cast to the caller's dtype, no quantisation) has its own tail
+// (EpiBq::split_tail_final).
 #pragma once
 #include "gemm_bq_persistent.cuh"
 

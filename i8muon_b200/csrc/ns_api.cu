@@ -658,11 +658,17 @@ extern "C" int i8m_bq_gemm(int fp8, int mode, const void* a, const float* sa, co
 // ====================================================== optimizer kernels
 extern "C" int i8m_momentum(const void* const* grads, void* const* bufs, int count, void* update,
                             long long numel, int dtype, float buf_weight, float mu, int nesterov,
-                            i8m_stream_t stream) {
+                            float* stats_partials, i8m_stream_t stream) {
   if (!grads || !bufs || !update || count < 1 || numel < 1 || !float_dtype_ok(dtype))
     return fail(I8M_E_ARGUMENT, "momentum: bad argument");
+  if (numel / STATS_CHUNK >= 0x7fffffffLL) return fail(I8M_E_LIMIT, "momentum: tensor too large");
   const size_t es = dtype_size(dtype);
-  const int blocks_x = int(std::min<long long>(cdiv(numel, 256 * 8), 148 * 16));
+  const int chunks = int(numel / STATS_CHUNK + (numel % STATS_CHUNK != 0));
+  const int blocks_x = std::min(chunks, 148 * 16);
+  // stats_partials (optional): the scratch layout of i8m_stats over the stacked update,
+  // [count][chunks] sums of squares followed by [count][chunks] maxima
+  float* psum = stats_partials;
+  float* pmax = stats_partials ? stats_partials + size_t(count) * chunks : nullptr;
   for (int first = 0; first < count; first += MT_MAX) {
     const int c = std::min(MT_MAX, count - first);
     MomentumTable tab;
@@ -674,7 +680,7 @@ extern "C" int i8m_momentum(const void* const* grads, void* const* bufs, int cou
     char* u = static_cast<char*>(update) + size_t(first) * numel * es;
     dim3 grid(blocks_x, c);
     DISPATCH_IN(dtype, T, (momentum_kernel<T><<<grid, 256, 0, S(stream)>>>(
-                              tab, reinterpret_cast<T*>(u), numel, buf_weight, mu, nesterov)));
+                              tab, reinterpret_cast<T*>(u), numel, buf_weight, mu, nesterov, psum, pmax, chunks, first)));
     LAUNCH_CHECK("momentum");
   }
   return 0;
@@ -769,6 +775,7 @@ struct NsCall {
   int route, dtype, batch, rows, cols, compute, steps, fp16_first;
   int factored = 0;   // coefficient rows are (c, p, q) of c * ((G + p I)^2 + q I)
   int deterministic = 1;   // 0: one-pass statistics with atomics (summation order not reproducible)
+  const float* stats_partials = nullptr;   // partials of the statistics over x, computed by the caller (i8m_momentum)
   int fuse_first_row = 1;   // fp16-first INT8-BQ: the first row's update quantises its own result
   int wholek[3] = {-1, -1, -1};   // global INT8: kernel variant of the Gram / square / update product (-1: thread's)
   const void* x;
@@ -782,6 +789,14 @@ struct NsCall {
 
 int call_stats(const NsCall& c, const void* x, int B, long long count, void* scratch, size_t sbytes, float* norm,
                float* amax) {
+  if (c.stats_partials && x == c.x) {
+    // the producer of x left the per-chunk partials: only the final fold remains
+    const int chunks = int(count / STATS_CHUNK + (count % STATS_CHUNK != 0));
+    stats_final_kernel<<<B, STATS_THREADS, 0, c.stream>>>(c.stats_partials, c.stats_partials + size_t(B) * chunks, norm,
+                                                          amax, chunks);
+    LAUNCH_CHECK("stats_final");
+    return 0;
+  }
   if (c.deterministic) return i8m_stats(x, c.dtype, B, count, scratch, sbytes, norm, amax, c.stream);
   return i8m_stats_onepass(x, c.dtype, B, count, scratch, sbytes, norm, amax, c.stream);
 }
@@ -1184,8 +1199,9 @@ extern "C" int i8m_ns_workspace_bytes(int route, int batch, int rows, int cols, 
 
 extern "C" int i8m_ns_run(int route, const void* x, void* out, int dtype, int batch, int rows,
                           int cols, int compute, const double* coeffs, int steps, float eps,
-                          int fp16_first, int deterministic, int variants, const char* gram_order, void* workspace,
-                          size_t workspace_bytes, uint32_t* status, i8m_stream_t stream) {
+                          int fp16_first, int deterministic, int variants, const char* gram_order,
+                          const float* stats_partials, void* workspace, size_t workspace_bytes, uint32_t* status,
+                          i8m_stream_t stream) {
   if (!x || !out || !coeffs || !workspace || !status) return fail(I8M_E_ARGUMENT, "ns_run: null pointer");
   if (x == out) return fail(I8M_E_ARGUMENT, "ns_run: out may not alias x");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
@@ -1200,6 +1216,7 @@ extern "C" int i8m_ns_run(int route, const void* x, void* out, int dtype, int ba
   c.x = x; c.out = out; c.coeffs = coeffs; c.eps = eps; c.gram_order = gram_order;
   c.status = status; c.stream = S(stream);
   c.deterministic = deterministic ? 1 : 0;
+  c.stats_partials = stats_partials;
   Bump ws(workspace, workspace_bytes, false);
   if (variants < 0) return ns_dispatch(c, ws, false);
   // this call's own kernel selection; the thread's setting comes back whatever happens

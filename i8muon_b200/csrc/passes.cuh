@@ -55,6 +55,10 @@ __device__ __forceinline__ float block_max_256(float v, float* sh) {
   return r;
 }
 
+// The partial of one chunk is defined by ONE mapping, shared with the momentum kernel (which computes the
+// partials of the update it writes, so that the statistics pass over it disappears): thread t takes the
+// elements 8 (t + 256 i) + e of the chunk, i = 0..3 outer, e = 0..7 inner, s = fma(v, v, s) in that order,
+// then the block tree.  Same mapping => bit-identical norms whichever kernel produced the partials.
 template <typename In>
 __global__ void __launch_bounds__(STATS_THREADS)
 stats_partial_kernel(const In* x, float* partial_sum, float* partial_max, long long count,
@@ -62,14 +66,17 @@ stats_partial_kernel(const In* x, float* partial_sum, float* partial_max, long l
   __shared__ float sh[8];
   const int b = blockIdx.y, chunk = blockIdx.x;
   const In* src = x + size_t(b) * count;
-  long long base = (long long)chunk * STATS_CHUNK;
+  const long long base = (long long)chunk * STATS_CHUNK;
   float s = 0.f, mx = 0.f;
-#pragma unroll 8
-  for (int i = 0; i < 32; ++i) {
-    long long idx = base + threadIdx.x + i * STATS_THREADS;
-    float v = idx < count ? load_f(src, size_t(idx)) : 0.f;
-    s = __fmaf_rn(v, v, s);
-    mx = fmaxf(mx, fabsf(v));
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const long long idx = base + 8 * (threadIdx.x + STATS_THREADS * i) + e;
+      const float v = idx < count ? load_f(src, size_t(idx)) : 0.f;
+      s = __fmaf_rn(v, v, s);
+      mx = fmaxf(mx, fabsf(v));
+    }
   }
   s = block_sum_256(s, sh);
   mx = block_max_256(mx, sh);
@@ -111,12 +118,15 @@ stats_onepass_kernel(const In* x, float* sumsq, unsigned* amax_bits, unsigned* a
   const In* src = x + size_t(b) * count;
   long long base = (long long)chunk * STATS_CHUNK;
   float s = 0.f, mx = 0.f;
-#pragma unroll 8
-  for (int i = 0; i < 32; ++i) {
-    long long idx = base + threadIdx.x + i * STATS_THREADS;
-    float v = idx < count ? load_f(src, size_t(idx)) : 0.f;
-    s = __fmaf_rn(v, v, s);
-    mx = fmaxf(mx, fabsf(v));
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const long long idx = base + 8 * (threadIdx.x + STATS_THREADS * i) + e;
+      const float v = idx < count ? load_f(src, size_t(idx)) : 0.f;
+      s = __fmaf_rn(v, v, s);
+      mx = fmaxf(mx, fabsf(v));
+    }
   }
   s = block_sum_256(s, sh);
   mx = block_max_256(mx, sh);
@@ -551,42 +561,72 @@ __device__ __forceinline__ float lerp_f(float start, float end, float w) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 momentum_kernel(MomentumTable tab, T* update, long long numel, float w_buf, float mu,
-                int nesterov) {
+                int nesterov, float* partial_sum, float* partial_max, int chunks, int first_tensor) {
+  __shared__ float sh[8];
   const int t = blockIdx.y;
   const T* g = static_cast<const T*>(tab.grad[t]);
   T* buf = static_cast<T*>(tab.buf[t]);
   T* u = update + size_t(t) * numel;
-  constexpr int VEC = 16 / int(sizeof(T));
-  const long long nvec = numel / VEC;
+  constexpr int VEC = 16 / int(sizeof(T));       // elements per 16-byte vector: 8 (16-bit) or 4 (FP32)
+  constexpr int PER8 = 8 / VEC;                   // vectors per group of eight elements
   const bool aligned = ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(buf) |
                          reinterpret_cast<uintptr_t>(u)) & 15u) == 0;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (aligned) {
-    for (; i < nvec; i += stride) {
-      uint4 gv = reinterpret_cast<const uint4*>(g)[i];
-      uint4 bv = reinterpret_cast<uint4*>(buf)[i];
-      uint4 uv;
-      const T* ge = reinterpret_cast<const T*>(&gv);
-      T* be = reinterpret_cast<T*>(&bv);
-      T* ue = reinterpret_cast<T*>(&uv);
+  // One chunk of STATS_CHUNK elements at a time, in the element order of stats_partial_kernel, so that the
+  // partial sums of squares and maxima of the update written here are the ones that kernel would compute.
+  for (int chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+    const long long base = (long long)chunk * STATS_CHUNK;
+    float s = 0.f, mx = 0.f;
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        const float gf = widen<T>(ge[e]);
-        const T nb = round_to<T>(lerp_f(widen<T>(be[e]), gf, w_buf));
-        be[e] = nb;
-        ue[e] = nesterov ? round_to<T>(lerp_f(gf, widen<T>(nb), mu)) : nb;
+    for (int i = 0; i < 4; ++i) {
+      const long long e0 = base + 8 * (threadIdx.x + STATS_THREADS * i);   // first of this thread's eight elements
+      if (aligned && e0 + 8 <= numel) {
+#pragma unroll
+        for (int v = 0; v < PER8; ++v) {
+          const long long vi = e0 / VEC + v;
+          uint4 gv = reinterpret_cast<const uint4*>(g)[vi];
+          uint4 bv = reinterpret_cast<uint4*>(buf)[vi];
+          uint4 uv;
+          const T* ge = reinterpret_cast<const T*>(&gv);
+          T* be = reinterpret_cast<T*>(&bv);
+          T* ue = reinterpret_cast<T*>(&uv);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            const float gf = widen<T>(ge[e]);
+            const T nb = round_to<T>(lerp_f(widen<T>(be[e]), gf, w_buf));
+            be[e] = nb;
+            ue[e] = nesterov ? round_to<T>(lerp_f(gf, widen<T>(nb), mu)) : nb;
+            const float uf = widen<T>(ue[e]);
+            s = __fmaf_rn(uf, uf, s);
+            mx = fmaxf(mx, fabsf(uf));
+          }
+          reinterpret_cast<uint4*>(buf)[vi] = bv;
+          reinterpret_cast<uint4*>(u)[vi] = uv;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const long long idx = e0 + e;
+          if (idx < numel) {
+            const float gf = widen<T>(g[idx]);
+            const T nb = round_to<T>(lerp_f(widen<T>(buf[idx]), gf, w_buf));
+            buf[idx] = nb;
+            const T un = nesterov ? round_to<T>(lerp_f(gf, widen<T>(nb), mu)) : nb;
+            u[idx] = un;
+            const float uf = widen<T>(un);
+            s = __fmaf_rn(uf, uf, s);
+            mx = fmaxf(mx, fabsf(uf));
+          }
+        }
       }
-      reinterpret_cast<uint4*>(buf)[i] = bv;
-      reinterpret_cast<uint4*>(u)[i] = uv;
     }
-    i = nvec * VEC + (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  }
-  for (; i < numel; i += stride) {
-    const float gf = widen<T>(g[i]);
-    const T nb = round_to<T>(lerp_f(widen<T>(buf[i]), gf, w_buf));
-    buf[i] = nb;
-    u[i] = nesterov ? round_to<T>(lerp_f(gf, widen<T>(nb), mu)) : nb;
+    if (partial_sum) {   // uniform per launch
+      s = block_sum_256(s, sh);
+      mx = block_max_256(mx, sh);
+      if (threadIdx.x == 0) {
+        partial_sum[size_t(first_tensor + t) * chunks + chunk] = s;
+        partial_max[size_t(first_tensor + t) * chunks + chunk] = mx;
+      }
+    }
   }
 }
 

@@ -122,7 +122,7 @@ class CutlassNSInt8:
 
     # ------------------------------------------------------------- launch
     def _run(self, route, x, coeffs, eps, compute, alignment, spec_precision, fp16_first, out=None,
-             deterministic=True):
+             deterministic=True, stats=None):
         coeffs = DEFAULT_COEFFICIENTS if coeffs is None else coeffs
         shape = x.shape
         batch, rows, cols, *_ = matrix_spec(tuple(shape), x.dtype, x.device, spec_precision, alignment)
@@ -139,51 +139,70 @@ class CutlassNSInt8:
             elif (out.shape != x.shape or out.dtype != x.dtype or out.device != x.device
                   or not out.is_contiguous() or out.data_ptr() == x.data_ptr()):
                 raise ValueError("out must be a contiguous tensor like x that does not alias it")
+            if stats is not None and (stats.dtype != torch.float32 or stats.device != x.device or not stats.is_contiguous()
+                                      or stats.numel() * 4 < native.stats_scratch_bytes(batch, rows * cols)):
+                raise ValueError("stats must be the FP32 partials that i8m_momentum left for x")
 
             def launch(variant):
                 workspace = torch.empty(size, dtype=torch.uint8, device=x.device)
                 native.call("i8m_ns_run", route, x.data_ptr(), out.data_ptr(), dtype, batch, rows, cols,
                             compute, array, steps, float(eps), int(bool(fp16_first)), int(bool(deterministic)),
                             int(variant),
-                            order.encode() if order is not None else None, workspace.data_ptr(), size,
+                            order.encode() if order is not None else None,
+                            stats.data_ptr() if stats is not None else None, workspace.data_ptr(), size,
                             status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
 
             variant = 0
+            key = (x.device.index, x.dtype, batch, rows, cols, route, compute, steps, bool(fp16_first))
             if route in (native.ROUTE_INT8, native.ROUTE_INT8_FACTORED) and self.tiles:
                 # explicit tiles take precedence over measurements, as in the reference
                 per_op = [0 if self.tiles.get(op, 4) == 4 else 1 for op in ("aat", "square", "update")]
                 variant = (per_op[0] << 8) | (per_op[1] << 16) | (per_op[2] << 24)
-            if route in (native.ROUTE_BQ_INT8, native.ROUTE_BQ_FP8):
-                key = (x.device.index, x.dtype, batch, rows, cols, route, steps, bool(fp16_first))
-                variant = self._factory.select("bq_gemm", key, tuple(range(native.variant_count("bq_gemm"))), 0, launch)
+            elif self._factory.autotune:
+                # per operation first (median of three graph replays, >= 2 % to replace the default), then the
+                # tuned call as a whole against the all-default call (>= 1 %), as the reference's factory does
+                tuned = 0
+                if route in (native.ROUTE_BQ_INT8, native.ROUTE_BQ_FP8):
+                    tuned = self._factory.select("bq_gemm", key, tuple(range(native.variant_count("bq_gemm"))), 0, launch)
+                if route != native.ROUTE_BQ_FP8 and not (route == native.ROUTE_FLOAT and compute == native.F32):
+                    # routes with whole-K products (the FP16 first row included): bits 8.. select their kernel
+                    choice = self._factory.select("wholek_gemm", key, (0, 1), 0,
+                                                  lambda v: launch(tuned | (v << 8) | (v << 16) | (v << 24)))
+                    tuned |= (choice << 8) | (choice << 16) | (choice << 24)
+                if tuned and self._factory.select_pipeline("ns_call", key, lambda use: launch(tuned if use else 0)):
+                    variant = tuned
             launch(variant)
         # The workspace may be reused by later allocations on this stream only.
         return out.view(shape)
 
-    # Every entry point takes the reference's arguments plus a keyword-only ``out``: a caller-owned
-    # tensor for the result (the sharded step lets NS write straight into its gather buffer).
-    def _regular_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16", *, out=None):
+    # Every entry point takes the reference's arguments plus two keyword-only extras: ``out``, a caller-owned
+    # tensor for the result (the sharded step lets NS write straight into its gather buffer), and ``stats``,
+    # the statistics partials that the momentum kernel left for ``x`` (then no pass over ``x`` is needed
+    # for its norm).
+    def _regular_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16", *, out=None, stats=None):
         """FP32 / BF16 / FP16 regular NS (src/i8muon/_cutlass_prec.py:90-106)."""
         precision = normalize_precision(precision)
         if precision not in _COMPUTE_CODES:
             raise ValueError(f"Unsupported floating-point precision: {precision}")
         return self._run(native.ROUTE_FLOAT, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False, out,
-                         deterministic)
+                         deterministic, stats)
 
-    def _gram_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16", *, out=None):
+    def _gram_prec(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float16", *, out=None, stats=None):
         """Gram-space NS with restarts given by I8MUON_GRAM_RESET (src/i8muon/_cutlass_prec.py:107-130)."""
         precision = normalize_precision(precision)
         if precision not in _COMPUTE_CODES:
             raise ValueError(f"Unsupported floating-point precision: {precision}")
         return self._run(native.ROUTE_GRAM, x, coeffs, eps, _COMPUTE_CODES[precision], 16, precision, False, out,
-                         deterministic)
+                         deterministic, stats)
 
-    def _regular_i8(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="int8", *, block=False, out=None):
+    def _regular_i8(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="int8", *, block=False, out=None,
+                    stats=None):
         """Global-scale INT8 NS, optionally after one FP16 iteration (src/i8muon/_cutlass.py:130-142)."""
         if block:
             return self._run(native.ROUTE_BQ_INT8, x, coeffs, eps, native.F16, 128, "int8", self.fp16_first, out,
-                             deterministic)
-        return self._run(native.ROUTE_INT8, x, coeffs, eps, native.F16, 16, "int8", self.fp16_first, out, deterministic)
+                             deterministic, stats)
+        return self._run(native.ROUTE_INT8, x, coeffs, eps, native.F16, 16, "int8", self.fp16_first, out, deterministic,
+                         stats)
 
     # ------------------------------------------------ opt-in polynomial entry points
     def _regular_i8_factored(self, X, factor_rows, eps=1e-7, deterministic=True, *, out=None):
@@ -209,15 +228,17 @@ class CutlassNSInt8:
         from .polynomial import cubic_abc
         return cubic_abc(self, X, coeffs, eps)
 
-    def _regular_bq(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float8_e4m3fn", *, out=None):
+    def _regular_bq(self, x, coeffs=None, eps=1e-7, deterministic=True, precision="float8_e4m3fn", *, out=None,
+                    stats=None):
         """128x128 block-quantised NS: INT8 honours fp16_first, E4M3 never does
         (src/i8muon/_cutlass.py:71-76)."""
         precision = normalize_precision(precision)
         if precision in ("int8_bq", "int8"):
-            return self._regular_i8(x, coeffs, eps, deterministic, "int8", block=True, out=out)
+            return self._regular_i8(x, coeffs, eps, deterministic, "int8", block=True, out=out, stats=stats)
         if precision != "float8_e4m3fn":
             raise ValueError(f"Unsupported block-quantised precision: {precision}")
-        return self._run(native.ROUTE_BQ_FP8, x, coeffs, eps, native.F16, 128, precision, False, out, deterministic)
+        return self._run(native.ROUTE_BQ_FP8, x, coeffs, eps, native.F16, 128, precision, False, out, deterministic,
+                         stats)
 
 
 __all__ = ["CutlassNSInt8", "check_status", "status_word", "post_status", "raise_if_reported"]

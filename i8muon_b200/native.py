@@ -58,9 +58,9 @@ _SIGNATURES = {
     "i8m_ns_workspace_bytes": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                        POINTER(c_size_t)]),
     "i8m_ns_run": (c_int, [c_int, _P, _P, c_int, c_int, c_int, c_int, c_int, POINTER(c_double),
-                           c_int, c_float, c_int, c_int, c_int, c_char_p, _P, c_size_t, _P, _P]),
+                           c_int, c_float, c_int, c_int, c_int, c_char_p, _P, _P, c_size_t, _P, _P]),
     "i8m_momentum": (c_int, [POINTER(_P), POINTER(_P), c_int, _P, c_longlong, c_int, c_float,
-                             c_float, c_int, _P]),
+                             c_float, c_int, _P, _P]),
     "i8m_apply": (c_int, [POINTER(_P), c_int, _P, c_longlong, c_int, c_int, c_int, c_float,
                           c_float, _P]),
     "i8m_adamw": (c_int, [POINTER(_P), POINTER(_P), POINTER(_P), POINTER(_P), POINTER(c_longlong), c_int,

@@ -262,12 +262,19 @@ def _as_float(value) -> float:
     return float(value.item()) if isinstance(value, Tensor) else float(value)
 
 
-def _momentum(grads, bufs, update, w_buf, mu, nesterov):
-    """buf <- lerp(buf, grad, w_buf); update[i] <- lerp(grad, buf, mu) (Nesterov) or buf: one launch per 32 tensors."""
+def _stats_buffer(count, numel, device):
+    """FP32 tensor for the statistics partials of ``count`` stacked tensors of ``numel`` elements."""
+    return torch.empty(native.stats_scratch_bytes(count, numel) // 4, dtype=torch.float32, device=device)
+
+
+def _momentum(grads, bufs, update, w_buf, mu, nesterov, stats=None):
+    """buf <- lerp(buf, grad, w_buf); update[i] <- lerp(grad, buf, mu) (Nesterov) or buf: one launch per 32
+    tensors.  ``stats`` receives the partial sums of squares and maxima of the update, so that the
+    Newton-Schulz call that follows needs no pass over it for its norm."""
     native.call("i8m_momentum", native.pointer_array([g.data_ptr() for g in grads]),
                 native.pointer_array([b.data_ptr() for b in bufs]), len(grads), update.data_ptr(),
                 grads[0].numel(), native.torch_dtype_code(update.dtype), w_buf, mu, int(nesterov),
-                torch.cuda.current_stream().cuda_stream)
+                stats.data_ptr() if stats is not None else None, torch.cuda.current_stream().cuda_stream)
 
 
 def muon_step(
@@ -326,6 +333,9 @@ def muon_step(
         native.torch_dtype_code(gdtype)
         adjusted = adjust_lr(lr, adjust_lr_fn, shape)
         ns_kwargs = dict(coeffs=ns_coefficients, eps=eps, deterministic=deterministic, precision=actual)
+        # this library's engine takes the statistics partials that the momentum kernel leaves; a foreign
+        # engine with the reference's call convention does not
+        takes_stats = isinstance(ns_engine, CutlassNSInt8) and deterministic and len(shape) == 2
         per_tensor = 1
         for d in shape:
             per_tensor *= d
@@ -356,23 +366,26 @@ def muon_step(
                         # so neither re-allocated gradients nor a learning-rate schedule invalidates it.
                         update = torch.empty((count, *shape), device=device, dtype=gdtype)
                         update.zero_()
+                        stats = _stats_buffer(count, per_tensor, device).zero_() if takes_stats else None
+                        extra = dict(stats=stats) if takes_stats else {}
                         for _ in range(2):   # warm up outside capture: first-use work, the tuner, workspaces
-                            ns_fn(update, **ns_kwargs)
+                            ns_fn(update, **ns_kwargs, **extra)
                         torch.cuda.current_stream().synchronize()
                         graph = torch.cuda.CUDAGraph()
                         with torch.cuda.graph(graph):
-                            ortho = ns_fn(update, **ns_kwargs)
-                        captured = (graph, update, ortho)
+                            ortho = ns_fn(update, **ns_kwargs, **extra)
+                        captured = (graph, update, ortho, stats)
                     ns_graphs[key] = captured            # most recently used last
                     while len(ns_graphs) > MAX_CAPTURED_GRAPHS:
                         ns_graphs.pop(next(iter(ns_graphs)))
-                    graph, update, ortho = captured
-                    _momentum(g_list, b_list, update, 1.0 - mu2, mu, nesterov)
+                    graph, update, ortho, stats = captured
+                    _momentum(g_list, b_list, update, 1.0 - mu2, mu, nesterov, stats)
                     graph.replay()
                 else:
                     update = torch.empty((count, *shape), device=device, dtype=gdtype)
-                    _momentum(g_list, b_list, update, 1.0 - mu2, mu, nesterov)
-                    ortho = ns_fn(update, **ns_kwargs)
+                    stats = _stats_buffer(count, per_tensor, device) if takes_stats else None
+                    _momentum(g_list, b_list, update, 1.0 - mu2, mu, nesterov, stats)
+                    ortho = ns_fn(update, **ns_kwargs, **(dict(stats=stats) if takes_stats else {}))
 
                 if callable(adjust_lr_fn):
                     adjusted = adjust_lr(lr, adjust_lr_fn, shape)
@@ -406,15 +419,22 @@ def native_step_ops(ns_engine: CutlassNSInt8, *, lr, weight_decay, momentum, ns_
     mu, mu2 = float(momentum[0]), float(momentum[-1])
     precision = normalize_precision(precision)
 
-    def do_momentum(grads, bufs, out):
-        native.call("i8m_momentum", native.pointer_array([g.data_ptr() for g in grads]),
-                    native.pointer_array([b.data_ptr() for b in bufs]), len(grads), out.data_ptr(),
-                    grads[0].numel(), native.torch_dtype_code(out.dtype), 1.0 - mu2, mu, int(nesterov),
-                    torch.cuda.current_stream().cuda_stream)
+    partials = {}     # (device, count, numel) -> statistics partials, reused from step to step
 
-    def do_ns(x, out=None):
+    def do_momentum(grads, bufs, out):
+        if grads[0].ndim != 2:        # leading dimensions fold into the batch: the partials are per tensor
+            _momentum(grads, bufs, out[:len(grads)], 1.0 - mu2, mu, nesterov)
+            return None
+        key = (out.device, len(grads), grads[0].numel())
+        stats = partials.get(key)
+        if stats is None:
+            stats = partials[key] = _stats_buffer(len(grads), grads[0].numel(), out.device)
+        _momentum(grads, bufs, out[:len(grads)], 1.0 - mu2, mu, nesterov, stats)
+        return stats
+
+    def do_ns(x, out=None, stats=None):
         fn, actual = ns_engine.router(x.shape[-2], x.shape[-1], precision, use_gram, gram_aspect_threshold)
-        return fn(x, coeffs=ns_coefficients, eps=eps, deterministic=True, precision=actual, out=out)
+        return fn(x, coeffs=ns_coefficients, eps=eps, deterministic=True, precision=actual, out=out, stats=stats)
 
     def do_apply(params, updates):
         shape = params[0].shape

@@ -101,7 +101,8 @@ def build_plan(shapes: Sequence[Sequence[int]], keys: Sequence[Tuple], world: in
 
 @dataclass
 class StepOps:
-    """momentum(grads, bufs, out): write stacked updates of len(grads) matrices into out[:len(grads)].
+    """momentum(grads, bufs, out): write stacked updates of len(grads) matrices into out[:len(grads)]; it
+    may return statistics of what it wrote, which are handed to orthogonalise as ``stats=`` if that takes it.
     orthogonalise(x) -> same shape; if it takes ``out=``, the result is written there (the step
     then lets it write straight into the gather buffer and gathers in place).
     apply(params, updates): updates is (len(params), *shape)."""
@@ -142,6 +143,7 @@ class ShardedMuonStep:
         self._staging: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._copy_stream = None
         self._ns_takes_out = "out" in inspect.signature(ops.orthogonalise).parameters
+        self._ns_takes_stats = "stats" in inspect.signature(ops.orthogonalise).parameters
         self._consumed: Dict[int, object] = {}   # chunk -> event: its gradients were read
         self._chunk_list = self._plan_chunks(params)
         self._flat: Dict[int, torch.Tensor] = {}
@@ -254,7 +256,8 @@ class ShardedMuonStep:
                 if ready is not None and ready[c] is not None:
                     torch.cuda.current_stream(like.device).wait_event(ready[c])
                 end = self._mark(phases, c, "momentum", like.device)
-                self.ops.momentum([grads[i] for i in mine], [buffers[i] for i in mine], send)
+                stats = self.ops.momentum([grads[i] for i in mine], [buffers[i] for i in mine], send)
+                extra = dict(stats=stats) if (self._ns_takes_stats and stats is not None) else {}
                 if end is not None:
                     end.record()
                 if like.device.type == "cuda":
@@ -266,15 +269,15 @@ class ShardedMuonStep:
                 end = self._mark(phases, c, "newton_schulz", like.device)
                 if flat is not None:
                     if self._ns_takes_out:
-                        self.ops.orthogonalise(send[:len(mine)], out=ortho[:len(mine)])
+                        self.ops.orthogonalise(send[:len(mine)], out=ortho[:len(mine)], **extra)
                         result = ortho[:len(mine)]
                     else:
-                        result = self.ops.orthogonalise(send[:len(mine)])
+                        result = self.ops.orthogonalise(send[:len(mine)], **extra)
                 elif self._ns_takes_out:
                     own = recv[self.rank * width:self.rank * width + len(mine)]
-                    self.ops.orthogonalise(send[:len(mine)], out=own)
+                    self.ops.orthogonalise(send[:len(mine)], out=own, **extra)
                 else:
-                    send[:len(mine)].copy_(self.ops.orthogonalise(send[:len(mine)]))
+                    send[:len(mine)].copy_(self.ops.orthogonalise(send[:len(mine)], **extra))
                 if end is not None:
                     end.record()
                 if flat is not None:

@@ -202,6 +202,7 @@ int i8m_bq_gemm(int fp8, int mode, const void* a, const float* sa, const float* 
  *                product << 24), bits 8-15 then being the Gram product's; the thread's own choices
  *                are untouched
  *   gram_order   GRAM route: restart string such as "00100" (NULL = default)
+ *   stats_partials  NULL, or the partials that i8m_momentum left for x (same batch and element count)
  *   workspace    device memory of at least i8m_ns_workspace_bytes(...) bytes,
  *                256-byte aligned; contents are scratch
  */
@@ -209,17 +210,21 @@ int i8m_ns_workspace_bytes(int route, int batch, int rows, int cols, int dtype, 
                            int steps, int fp16_first, size_t* bytes);
 int i8m_ns_run(int route, const void* x_device, void* out_device, int dtype, int batch, int rows,
                int cols, int compute, const double* coeffs, int steps, float eps, int fp16_first,
-               int deterministic, int variants, const char* gram_order, void* workspace_device, size_t workspace_bytes,
+               int deterministic, int variants, const char* gram_order, const float* stats_partials_device, void* workspace_device, size_t workspace_bytes,
                uint32_t* status_device, i8m_stream_t stream);
 
 /* ---- optimizer step kernels ------------------------------------------------
  * momentum: buf <- lerp(buf, grad, 1 - mu2); update = nesterov ? lerp(grad, buf, mu) : buf
  * for `count` same-shaped tensors given as host arrays of device pointers; the
  * updates are written stacked into update_device (count x numel).  Replaces
- * src/i8muon/_optimizer.py:472-474. */
+ * src/i8muon/_optimizer.py:472-474.  stats_partials (optional, i8m_stats_scratch_bytes(count, numel) bytes):
+ * the kernel also leaves the per-chunk sums of squares and maxima of the update it writes, in the scratch
+ * layout of i8m_stats; handed to i8m_ns_run they replace its statistics pass over the update (the torch
+ * norm of src/i8muon/_cutlass_prec.py:66-73, _cutlass.py:190, _cutlass_bq.py:42) by the final fold alone,
+ * with a bit-identical norm. */
 int i8m_momentum(const void* const* grads, void* const* bufs, int count, void* update_device,
                  long long numel, int dtype, float buf_weight, float mu, int nesterov,
-                 i8m_stream_t stream);
+                 float* stats_partials_device, i8m_stream_t stream);
 /* apply: decay_mode 0 none, 1 param *= decay, 2 update += decay * param; then
  * param += neg_lr * update.  Replaces src/i8muon/_optimizer.py:503-511. */
 int i8m_apply(void* const* params, int count, const void* update_device, long long numel,

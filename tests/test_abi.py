@@ -60,9 +60,9 @@ def test_argument_errors_are_codes_not_crashes(lib):
         assert lib.i8m_ns_workspace_bytes(*args, ctypes.byref(size)) == -1
         assert lib.i8m_last_error()
     with pytest.raises(native.NativeError, match="null"):
-        native.call("i8m_ns_run", 0, None, None, 0, 1, 8, 8, 1, None, 5, 1e-7, 0, 1, -1, None, None, 0, None, None)
+        native.call("i8m_ns_run", 0, None, None, 0, 1, 8, 8, 1, None, 5, 1e-7, 0, 1, -1, None, None, None, 0, None, None)
     with pytest.raises(native.NativeError):
-        native.call("i8m_momentum", None, None, 0, None, 0, 0, 0.0, 0.0, 0, None)
+        native.call("i8m_momentum", None, None, 0, None, 0, 0, 0.0, 0.0, 0, None, None)
     with pytest.raises(native.NativeError):
         native.call("i8m_bq_gemm", 0, 0, 1, 1, None, 1, 1, None, 1, None, None, None, 1, 100, 128, 128, 100,
                     128, 0.0, 0.0, 0.0, 0, 0, 0, None, None)

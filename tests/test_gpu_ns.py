@@ -278,9 +278,11 @@ def test_autotuned_engine_and_kernel_variants_give_identical_results(cuda_device
     got = tuned._regular_bq(x, C5, precision="int8_bq")
     check_status()
     assert torch.equal(got, want)
-    assert len(tuned._factory.timings) == 1
-    (scores,) = tuned._factory.timings.values()
-    assert set(scores) == {0, 1, 2} and all(v > 0 for v in scores.values())
+    timings = {key[0]: scores for key, scores in tuned._factory.timings.items()}
+    assert set(timings["bq_gemm"]) == {0, 1, 2} and all(v > 0 for v in timings["bq_gemm"].values())
+    assert set(timings["wholek_gemm"]) == {0, 1}     # the FP16 first row's products
+    tuned._regular_bq(x, C5, precision="int8_bq")     # second call: every choice comes from the cache
+    assert {key[0] for key in tuned._factory.timings} == set(timings)
     with pytest.raises(native.NativeError):
         native.call("i8m_set_variant", b"no_such_op", 0)
 

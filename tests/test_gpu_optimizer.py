@@ -21,7 +21,7 @@ def fused_step(p, b, g, case):
     mu, mu2 = momentum[0], momentum[-1]
     update = torch.empty((1, *g.shape), device=g.device, dtype=g.dtype)
     native.call("i8m_momentum", native.pointer_array([g.data_ptr()]), native.pointer_array([b.data_ptr()]), 1,
-                update.data_ptr(), g.numel(), H.DT[g.dtype], 1.0 - mu2, mu, int(len(momentum) == 2), stream)
+                update.data_ptr(), g.numel(), H.DT[g.dtype], 1.0 - mu2, mu, int(len(momentum) == 2), None, stream)
     ortho = (update.float() * 3.0).to(update.dtype)
     lr, wd = case["lr"], case["wd"]
     adjusted = o.adjust_lr(lr, case["adjust"], p.shape)
@@ -329,3 +329,36 @@ def test_a_reported_status_word_raises_at_the_next_step(cuda_device):
     assert int(status_word(cuda_device).item()) == 0
     opt.step()                                   # cleared: training can go on (or stop) by the caller's choice
     check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(300, 517), (64, 128), (1024, 4096)])
+def test_momentum_kernel_leaves_the_statistics_of_its_update(cuda_device, dtype, shape):
+    """The partial sums of squares and maxima that ``i8m_momentum`` writes for the update are the ones the
+    statistics pass computes over the same tensor (one chunk mapping for both kernels), so the norm that
+    Newton-Schulz takes from them is bit-identical and the entry point gives the same result with or without."""
+    dev = cuda_device
+    g = torch.Generator().manual_seed(3)
+    count = 3
+    grads = [(torch.randn(shape, generator=g) * 1e-3).to(dtype).to(dev) for _ in range(count)]
+    bufs = [(torch.randn(shape, generator=g) * 1e-3).to(dtype).to(dev) for _ in range(count)]
+    numel = grads[0].numel()
+    update = torch.empty((count, *shape), device=dev, dtype=dtype)
+    stats = torch.full((native.stats_scratch_bytes(count, numel) // 4,), float("nan"), device=dev)
+    native.call("i8m_momentum", native.pointer_array([t.data_ptr() for t in grads]),
+                native.pointer_array([t.data_ptr() for t in bufs]), count, update.data_ptr(), numel, H.DT[dtype],
+                0.05, 0.95, 1, stats.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    # the statistics pass over the update, partials included
+    nbytes = native.stats_scratch_bytes(count, numel)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    norm, amax = torch.empty(count, device=dev), torch.empty(count, device=dev)
+    native.call("i8m_stats", update.data_ptr(), H.DT[dtype], count, numel, scratch.data_ptr(), nbytes, norm.data_ptr(),
+                amax.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert torch.equal(stats, scratch.view(torch.float32))
+    engine = CutlassNSInt8()
+    plain = engine._regular_bq(update, C5, 1e-7, True, "int8_bq")
+    fed = engine._regular_bq(update, C5, 1e-7, True, "int8_bq", stats=stats)
+    check_status()
+    assert torch.equal(plain, fed)
+    with pytest.raises(ValueError, match="stats must be"):
+        engine._regular_bq(update, C5, 1e-7, True, "int8_bq", stats=stats[:2])

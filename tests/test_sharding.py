@@ -223,3 +223,23 @@ def test_sharded_state_dict_reloads_at_another_world_size_and_into_the_single_de
         assert sorted(seen) == list(range(9))
         for i, b in seen.items():
             assert torch.equal(b, want_bufs[i])
+
+
+def test_sharded_state_dict_loads_into_the_single_device_optimizer():
+    """The gathered state dict has the reference's layout (``state[i]["momentum_buffer"]`` per matrix and the
+    caller's ``param_groups``), so ``Muon.load_state_dict`` takes it as it takes its own."""
+    from i8muon_b200 import Muon
+    params, bufs, grads = make_problem()
+    ops = cpu_ops((0.95, 0.9), 0.02, 0.01, "base_lr", "spectral")
+    stepper = ShardedMuonStep(params, steps=5, ops=ops)
+    buffers = {i: bufs[i] for i in stepper.plan.owned(0)}
+    stepper.step(params, grads[0], buffers)
+    wrapped = [torch.nn.Parameter(p.clone()) for p in params]
+    muon = Muon(wrapped, lr=0.02, weight_decay=0.01, momentum=(0.95, 0.9))
+    full = stepper.state_dict(params, buffers, param_groups=muon.state_dict()["param_groups"])
+    muon.load_state_dict(full)
+    for i, p in enumerate(wrapped):
+        assert torch.equal(muon.state[p]["momentum_buffer"], buffers[i])
+    again = muon.state_dict()
+    assert sorted(again["state"]) == list(range(len(params)))
+    assert again["param_groups"][0]["weight_decay_mode"] == "base_lr"
