@@ -476,10 +476,11 @@ def dominant_kernel_roofline(dev, peaks, source, b=4):
                            "figure: the factor 2 is inferred from the INT8 : BF16 dense rate of the part"}
 
 
-def fp16_first_iteration_gemm(dev, peaks, source, b=2):
+def fp16_first_iteration_gemm(dev, peaks, source, b=2, variant=0):
     """Time the FP16 update GEMM of the first iteration alone (gate/up shape, transposed BF16 result)."""
     from i8muon_b200 import native
     from i8muon_b200.engine import status_word
+    native.call("i8m_set_variant", b"wholek_gemm", variant)
     lp, hp = 4096, 14336
     gen = torch.Generator(device=dev).manual_seed(6)
     q = (torch.randn((b, lp, lp), device=dev, generator=gen) * 0.05).half()
@@ -506,9 +507,100 @@ def fp16_first_iteration_gemm(dev, peaks, source, b=2):
     achieved = flops / seconds / 1e12
     peak = peaks["bf16_tflops_sustained"]
     return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-            "kernel": f"wholek_persistent_kernel<EpiFloat<half, final>> B={b} 4096x14336 (k=4096), transposed bf16 result",
+            "kernel": f"{('wholek_persistent_kernel', 'ns_gemm_kernel', 'wholek_wide_kernel')[variant]}"
+                      f"<EpiFloat<half, final>> B={b} 4096x14336 (k=4096), transposed bf16 result",
             "flops_per_launch": flops, "ms_per_launch": seconds * 1e3,
             "peak_source": f"bf16_tflops_sustained of MEASURED_PEAKS.json ({source})"}
+
+
+def single_kernel(dev, peaks, source, name, b=1):
+    """Time one GEMM kernel of the path alone (small cases for ncu): the block-quantised Gram and polynomial
+    products on a 4096 x 14336 matrix, the global-INT8 update product at 4096 x 4096, the 3xTF32 Gram
+    product of an FP32 1024 x 4096 matrix."""
+    from i8muon_b200 import native
+    from i8muon_b200.engine import status_word
+    gen = torch.Generator(device=dev).manual_seed(11)
+    stream = torch.cuda.current_stream().cuda_stream
+    status = status_word(dev).data_ptr()
+    keep = []
+
+    def rand_i8(*shape):
+        t = torch.randint(-127, 128, shape, device=dev, dtype=torch.int8, generator=gen)
+        keep.append(t)
+        return t
+
+    def rand_f(*shape, lo=1e-4, span=1e-3):
+        t = torch.rand(shape, device=dev, generator=gen) * span + lo
+        keep.append(t)
+        return t
+
+    if name in ("bq_gram", "bq_poly"):
+        lp, hp = 4096, 14336
+        k = hp if name == "bq_gram" else lp
+        a, sa = rand_i8(b, lp, k), rand_f(b, lp // 128, k // 128)
+        da = rand_f(b, lp, lo=0.5, span=0.5)
+        out = torch.empty((b, lp, lp), device=dev, dtype=torch.uint8)
+        so, dout = torch.empty((b, lp // 128, lp // 128), device=dev), torch.empty((b, lp), device=dev)
+        mode = 0 if name == "bq_gram" else 1
+
+        def launch():
+            native.call("i8m_bq_gemm", 0, mode, a.data_ptr(), sa.data_ptr(), da.data_ptr() if mode else None,
+                        a.data_ptr(), sa.data_ptr(), None, out.data_ptr(), None, so.data_ptr(), dout.data_ptr(), b,
+                        lp, lp, k, lp, lp, 3.0, -4.0, 2.0, 0, 0, 0, status, stream)
+        tiles = (lp // 128) * (lp // 128 + 1) // 2
+        flops = 2.0 * 128 * 128 * tiles * k * b
+        peak, sustained = 2.0 * peaks["bf16_tflops"], 2.0 * peaks["bf16_tflops_sustained"]
+        kernel = f"bq_split_kernel<EpiBq<int8, {'gram' if mode == 0 else 'polynomial'}>> B={b} 4096x4096 lower tiles (k={k})"
+    elif name == "i8_update":
+        lp = hp = 4096
+        p8, at, a8 = rand_i8(b, lp, lp), rand_i8(b, hp, lp), rand_i8(b, lp, hp)
+        ps, a_s, diag = rand_f(b), rand_f(b), rand_f(b, lp, lo=0.5, span=0.5)
+        out, mx = torch.empty((b, lp, hp), device=dev), torch.zeros(b, device=dev)
+
+        def launch():
+            native.call("i8m_i8_gemm", 2, p8.data_ptr(), at.data_ptr(), a8.data_ptr(), out.data_ptr(), mx.data_ptr(),
+                        ps.data_ptr(), a_s.data_ptr(), diag.data_ptr(), b, lp, hp, lp, lp, hp, 0.0, 0.0, 0, 0, 0,
+                        status, stream)
+        flops = 2.0 * lp * lp * hp * b
+        peak, sustained = 2.0 * peaks["bf16_tflops"], 2.0 * peaks["bf16_tflops_sustained"]
+        kernel = f"whole-K kernel<EpiI8<update>> B={b} 4096x4096 (k=4096), FP32 result + maximum"
+    elif name == "fp32_gram":
+        lp, hp = 1024, 4096
+        x = torch.randn((b, lp, hp), device=dev, generator=gen) * 0.02
+        hi = (x.view(torch.int32) & ~0x1FFF).view(torch.float32).contiguous()
+        lo = ((x - hi).view(torch.int32) & ~0x1FFF).view(torch.float32).contiguous()
+        out, out_lo = torch.empty((b, lp, lp), device=dev), torch.empty((b, lp, lp), device=dev)
+
+        def launch():
+            native.call("i8m_float_gemm", hi.data_ptr(), lo.data_ptr(), hi.data_ptr(), lo.data_ptr(), out.data_ptr(),
+                        None, out_lo.data_ptr(), None, native.F32, 0, b, lp, lp, hp, lp, lp, 1, 0, 0, 0, 0.0, 0.0,
+                        0.0, status, stream)
+        tiles = (lp // 128) * (lp // 128 + 1) // 2
+        flops = 2.0 * 128 * 128 * tiles * hp * b
+        # three TF32 products per FP32 product, TF32 at half the BF16 rate
+        peak, sustained = peaks["bf16_tflops"] / 6.0, peaks["bf16_tflops_sustained"] / 6.0
+        kernel = f"ns_gemm_kernel<EpiFloat<float, gram>> B={b} 1024x1024 lower tiles (k=4096), 3 x TF32"
+    else:
+        raise SystemExit(f"unknown kernel {name}")
+    for _ in range(3):
+        launch()
+    n = 10
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(n):
+        launch()
+    end.record()
+    torch.cuda.synchronize()
+    if int(status_word(dev).item()) != 0:
+        raise SystemExit("a kernel reported a timed-out wait")
+    seconds = start.elapsed_time(end) / 1e3 / n
+    achieved = flops / seconds / 1e12
+    return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "frac_of_sustained_peak": achieved / sustained, "kernel": kernel, "flops_per_launch": flops,
+            "ms_per_launch": seconds * 1e3,
+            "peak_source": f"from bf16_tflops (burst) of MEASURED_PEAKS.json ({source}); INT8 taken as 2 x BF16, "
+                           "3xTF32 as BF16 / 6"}
 
 
 def run_native(args):
@@ -688,11 +780,23 @@ def main():
                         help="only time the FP16 first-iteration update GEMM on B matrices (small case for ncu)")
     parser.add_argument("--only-roofline", type=int, default=0, metavar="B",
                         help="only time the dominant GEMM on B matrices of 4096x14336 (small case for ncu)")
+    parser.add_argument("--wholek-variant", type=int, default=0,
+                        help="with --only-fp16: whole-K kernel (0 two streams of 128x128 tiles, 1 one CTA per tile, "
+                             "2 units of 128x256)")
+    parser.add_argument("--only-kernel", choices=("bq_gram", "bq_poly", "i8_update", "fp32_gram"), default=None,
+                        help="only time this GEMM kernel alone (small case for ncu); --kernel-batch matrices")
+    parser.add_argument("--kernel-batch", type=int, default=1)
     args = parser.parse_args()
+    if args.only_kernel:
+        torch.cuda.set_device(0)
+        peaks, source = measured_peaks()
+        print(json.dumps(single_kernel(torch.device("cuda", 0), peaks, source, args.only_kernel, args.kernel_batch)))
+        return
     if args.only_fp16:
         torch.cuda.set_device(0)
         peaks, source = measured_peaks()
-        print(json.dumps(fp16_first_iteration_gemm(torch.device("cuda", 0), peaks, source, args.only_fp16)))
+        print(json.dumps(fp16_first_iteration_gemm(torch.device("cuda", 0), peaks, source, args.only_fp16,
+                                                   args.wholek_variant)))
         return
     if args.only_roofline:
         torch.cuda.set_device(0)

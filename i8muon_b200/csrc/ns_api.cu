@@ -10,6 +10,7 @@
 #include "gemm_bq_persistent.cuh"
 #include "gemm_bq_split.cuh"
 #include "gemm_wholek_persistent.cuh"
+#include "gemm_wholek_wide.cuh"
 #include "passes.cuh"
 
 #include <cstdarg>
@@ -30,7 +31,8 @@ thread_local char g_error[512] = "";
 // selection as an argument and restores the thread's own setting when it returns.
 thread_local int g_debug_simt = 0;
 thread_local int g_starve_producers = 0;   // test hook: see bq_produce
-thread_local int g_wholek_persistent = 1;   // 0: one CTA per tile (variant 1 of "wholek_gemm")
+constexpr int WHOLEK_VARIANTS = 3;
+thread_local int g_wholek_variant = 0;   // "wholek_gemm": 0 two streams of 128 x 128 tiles, 1 one CTA per tile, 2 units of 128 x 256
 // block-quantised GEMMs: 0 = split kernel (tail on its own warps, four-stage ring), 1 = fused tail with a
 // six-stage ring, 2 = fused tail with a four-stage ring; the host-side tuner chooses per shape
 thread_local int g_cta_limit = 0;   // persistent GEMM kernels launch at most this many CTAs (0: one per SM)
@@ -141,7 +143,16 @@ int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_
   }
   // products that accumulate their whole K extent in tensor memory: persistent kernel
   if constexpr (!Epi::BLOCKQ && Epi::PARTS == 1 && Epi::PROMOTE_KB == 0) {
-    if (!g_debug_simt && g_wholek_persistent) {
+    if (!g_debug_simt && g_wholek_variant == 2) {
+      constexpr size_t WSMEM = wholek_wide_smem_bytes<Epi>();
+      auto wk = wholek_wide_kernel<Epi>;
+      CUDA_TRY(cudaFuncSetAttribute(wk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(WSMEM)));
+      const long long units = (long long)wide_units_per_batch(g.tiles_m, g.tiles_n, sym) * batch;
+      wk<<<unsigned(std::min<long long>(units, sm_count())), WKW_THREADS, WSMEM, stream>>>(ma, mb, g, args);
+      LAUNCH_CHECK(name);
+      return 0;
+    }
+    if (!g_debug_simt && g_wholek_variant == 0) {
       constexpr size_t PSMEM = size_t(WKP_STAGES) * 2 * TILE_BYTES + sizeof(Ctrl) + 1024;
       auto pk = wholek_persistent_kernel<Epi>;
       CUDA_TRY(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PSMEM)));
@@ -282,7 +293,7 @@ extern "C" int i8m_set_cta_limit(int max_ctas) {
 }
 extern "C" int i8m_variant_count(const char* operation) {
   if (operation && std::strcmp(operation, "bq_gemm") == 0) return BQ_VARIANTS;
-  if (operation && std::strcmp(operation, "wholek_gemm") == 0) return 2;
+  if (operation && std::strcmp(operation, "wholek_gemm") == 0) return WHOLEK_VARIANTS;
   return 0;
 }
 extern "C" int i8m_set_variant(const char* operation, int variant) {
@@ -291,7 +302,7 @@ extern "C" int i8m_set_variant(const char* operation, int variant) {
   if (variant < 0 || variant >= i8m_variant_count(operation))
     return fail(I8M_E_ARGUMENT, "set_variant: %s has variants 0 to %d", operation, i8m_variant_count(operation) - 1);
   if (operation[0] == 'b') g_bq_variant = variant;
-  else g_wholek_persistent = variant == 0 ? 1 : 0;
+  else g_wholek_variant = variant;
   return 0;
 }
 
@@ -468,6 +479,15 @@ static int float_gemm_to_bq_typed(const void* left, const void* right_t, const F
   CUtensorMap ma, mb;
   if (int rc = make_operand_map(&ma, left, 2, k, m, batch)) return rc;
   if (int rc = make_operand_map(&mb, right_t, 2, k, n, batch)) return rc;
+  if (g_wholek_variant == 2) {
+    constexpr size_t WSMEM = wholek_wide_smem_bytes<Epi>();
+    auto wk = wholek_wide_kernel<Epi>;
+    CUDA_TRY(cudaFuncSetAttribute(wk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(WSMEM)));
+    const long long units = (long long)wide_units_per_batch(g.tiles_m, g.tiles_n, 0) * batch;
+    wk<<<unsigned(std::min<long long>(units, sm_count())), WKW_THREADS, WSMEM, stream>>>(ma, mb, g, args);
+    LAUNCH_CHECK("float_gemm_to_bq");
+    return 0;
+  }
   constexpr size_t SMEM = size_t(WKP_STAGES) * 2 * TILE_BYTES + sizeof(Ctrl) + Epi::TSM_BYTES + 1024;
   auto kernel = wholek_persistent_kernel<Epi>;
   CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM)));
@@ -964,9 +984,9 @@ int run_int8(const NsCall& c, Bump& ws, bool plan, const void* x, int steps, con
     float* gmax = maxima + size_t(3 * it) * B;
     float* pmax = gmax + B;
     float* ymax = pmax + B;
-    const int thread_wholek = g_wholek_persistent;
-    auto pick = [&](int op) { g_wholek_persistent = c.wholek[op] < 0 ? thread_wholek : (c.wholek[op] == 0 ? 1 : 0); };
-    struct Restore { int v; ~Restore() { g_wholek_persistent = v; } } restore{thread_wholek};
+    const int thread_wholek = g_wholek_variant;
+    auto pick = [&](int op) { g_wholek_variant = c.wholek[op] < 0 ? thread_wholek : c.wholek[op]; };
+    struct Restore { int v; ~Restore() { g_wholek_variant = v; } } restore{thread_wholek};
     pick(0);
     if (int rc = i8m_i8_gemm(0, a8, a8, nullptr, work, gmax, nullptr, nullptr, nullptr, B, lp, lp, hp, l,
                              l, 0, 0, 0, 0, 0, c.status, c.stream))
@@ -1222,14 +1242,14 @@ extern "C" int i8m_ns_run(int route, const void* x, void* out, int dtype, int ba
   // this call's own kernel selection; the thread's setting comes back whatever happens
   const int bq = variants & 0xff, wholek = (variants >> 8) & 0xff;
   const int wk_square = (variants >> 16) & 0xff, wk_update = (variants >> 24) & 0x7f;
-  if (bq >= BQ_VARIANTS || wholek >= 2 || wk_square >= 2 || wk_update >= 2)
+  if (bq >= BQ_VARIANTS || wholek >= WHOLEK_VARIANTS || wk_square >= WHOLEK_VARIANTS || wk_update >= WHOLEK_VARIANTS)
     return fail(I8M_E_ARGUMENT, "ns_run: unknown kernel variant 0x%x", variants);
-  const int saved_bq = g_bq_variant, saved_wholek = g_wholek_persistent;
+  const int saved_bq = g_bq_variant, saved_wholek = g_wholek_variant;
   g_bq_variant = bq;
-  g_wholek_persistent = wholek == 0 ? 1 : 0;
+  g_wholek_variant = wholek;
   c.wholek[0] = wholek; c.wholek[1] = wk_square; c.wholek[2] = wk_update;
   const int rc = ns_dispatch(c, ws, false);
   g_bq_variant = saved_bq;
-  g_wholek_persistent = saved_wholek;
+  g_wholek_variant = saved_wholek;
   return rc;
 }

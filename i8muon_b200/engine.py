@@ -105,6 +105,10 @@ class CutlassNSInt8:
         self.fp16_first = fp16_first
         self.autotune = autotune
         self.tiles = dict(tiles or {})
+        # kernel selection of calls that neither ``tiles`` nor the tuner decides, in i8m_ns_run's packing
+        # (block-quantised GEMM | whole-K GEMM << 8 | its square << 16 | its update << 24); 0: the defaults
+        # (environment I8MUON_B200_KERNEL_VARIANTS presets it: an integer, e.g. 0x02020200)
+        self.kernel_variants = int(os.environ.get("I8MUON_B200_KERNEL_VARIANTS", "0"), 0)
         if (set(self.tiles) - {"aat", "square", "update"}
                 or any(v not in (0, 1, 2, 3, 4) for v in self.tiles.values())):
             raise ValueError("tiles accepts aat/square/update with values 0/1/2/3/4")
@@ -152,7 +156,7 @@ class CutlassNSInt8:
                             stats.data_ptr() if stats is not None else None, workspace.data_ptr(), size,
                             status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
 
-            variant = 0
+            variant = self.kernel_variants
             key = (x.device.index, x.dtype, batch, rows, cols, route, compute, steps, bool(fp16_first))
             if route in (native.ROUTE_INT8, native.ROUTE_INT8_FACTORED) and self.tiles:
                 # explicit tiles take precedence over measurements, as in the reference
@@ -166,7 +170,7 @@ class CutlassNSInt8:
                     tuned = self._factory.select("bq_gemm", key, tuple(range(native.variant_count("bq_gemm"))), 0, launch)
                 if route != native.ROUTE_BQ_FP8 and not (route == native.ROUTE_FLOAT and compute == native.F32):
                     # routes with whole-K products (the FP16 first row included): bits 8.. select their kernel
-                    choice = self._factory.select("wholek_gemm", key, (0, 1), 0,
+                    choice = self._factory.select("wholek_gemm", key, tuple(range(native.variant_count("wholek_gemm"))), 0,
                                                   lambda v: launch(tuned | (v << 8) | (v << 16) | (v << 24)))
                     tuned |= (choice << 8) | (choice << 16) | (choice << 24)
                 if tuned and self._factory.select_pipeline("ns_call", key, lambda use: launch(tuned if use else 0)):

@@ -280,11 +280,47 @@ def test_autotuned_engine_and_kernel_variants_give_identical_results(cuda_device
     assert torch.equal(got, want)
     timings = {key[0]: scores for key, scores in tuned._factory.timings.items()}
     assert set(timings["bq_gemm"]) == {0, 1, 2} and all(v > 0 for v in timings["bq_gemm"].values())
-    assert set(timings["wholek_gemm"]) == {0, 1}     # the FP16 first row's products
+    assert set(timings["wholek_gemm"]) == {0, 1, 2}     # the FP16 first row's products
     tuned._regular_bq(x, C5, precision="int8_bq")     # second call: every choice comes from the cache
     assert {key[0] for key in tuned._factory.timings} == set(timings)
     with pytest.raises(native.NativeError):
         native.call("i8m_set_variant", b"no_such_op", 0)
+
+
+WHOLEK_CASES = [
+    ("float", (4, 768, 3072), torch.bfloat16, "bfloat16"),     # 6 x 6 Gram tiles per matrix, 24 update columns
+    ("float", (2, 640, 1500), torch.float16, "float16"),       # odd tile counts: every row of units ends in a single tile
+    ("float", (1, 1500, 640), torch.bfloat16, "float16"),      # tall: transposed final store
+    ("gram", (2, 384, 2048), torch.float16, "float16"),
+    ("int8", (1, 1100, 1300), torch.bfloat16, None),           # global INT8 with its FP16 first row
+    ("bq", (1, 1536, 2048), torch.bfloat16, None),             # first row that block-quantises its own result
+    ("bq", (1, 2100, 1500), torch.bfloat16, None),
+]
+
+
+@pytest.mark.parametrize("route,shape,dtype,precision", WHOLEK_CASES)
+def test_wholek_kernel_variants_agree_bit_for_bit(cuda_device, route, shape, dtype, precision):
+    """The three whole-K kernels (two streams of 128 x 128 tiles, one CTA per tile, 128 x 256 units) accumulate
+    every output element over K in the same order, so whole NS calls agree bit for bit between them."""
+    assert native.variant_count("wholek_gemm") == 3
+    x = make(shape, dtype, 57, std=1e-3).to(cuda_device)
+    engine = CutlassNSInt8()
+    results = []
+    for variant in range(3):
+        engine.kernel_variants = (variant << 8) | (variant << 16) | (variant << 24)
+        if route == "float":
+            y = engine._regular_prec(x, C5, precision=precision)
+        elif route == "gram":
+            y = engine._gram_prec(x, C5, precision=precision)
+        elif route == "int8":
+            y = engine._regular_i8(x, C5)
+        else:
+            y = engine._regular_bq(x, C5, precision="int8_bq")
+        check_status()
+        results.append(y)
+    assert torch.isfinite(results[0]).all()
+    for other in results[1:]:
+        assert torch.equal(results[0], other)
 
 
 # completed squares of the first three rows of the default schedule: a + b g + c g^2 = c((g + p)^2 + q)
