@@ -50,6 +50,7 @@ struct GemmGeom {
   int tiles_per_batch;
   int num_kb;           // K blocks of 128 bytes
   int debug_simt;
+  int group;            // row blocks per group of the wide-unit order (even; set by the launcher)
   const void* a_raw;    // raw operand pointers (debug core and epilogue reads)
   const void* b_raw;
   unsigned* status;

@@ -36,28 +36,48 @@ __host__ __device__ inline int wide_units_per_batch(int tiles_m, int tiles_n, in
   return sym ? wide_units_before_row(tiles_m) : tiles_m * ((tiles_n + 1) / 2);
 }
 
+// Order of the units.  Row blocks are taken in groups of g.group and a group is walked column by
+// column, so the units in flight (one per SM, consecutive indices) share the group's left row
+// blocks, which stay in L2 for the whole sweep, and the right operand streams through once per
+// group.  (In plain row-major order of the triangle, row i of a symmetric product re-reads row
+// blocks 0..i of the right operand, a cyclic pattern that an LRU cache larger than L2 never hits.)
+// In a symmetric product a group of rows r0 .. r0 + R - 1 has r0 / 2 + 1 full columns of units and
+// then columns of R - 2, R - 4, ... units (rows tm >= 2 tw only).
 __device__ __forceinline__ void decode_unit(const GemmGeom& g, int units_per_batch, int linear, int& b, int& tm,
                                             int& tn, int& width) {
   b = linear / units_per_batch;
-  const int u = linear - b * units_per_batch;
+  int u = linear - b * units_per_batch;
+  const int group = g.group;   // even, >= 2
   if (g.sym) {
+    // the group that holds u: groups are whole rows, so the row search of the triangle finds it
     int i = min(g.tiles_m - 1, int(2.f * sqrtf(float(u))));
     while (i + 1 < g.tiles_m && wide_units_before_row(i + 1) <= u) ++i;
     while (i > 0 && wide_units_before_row(i) > u) --i;
-    tm = i;
-    tn = 2 * (u - wide_units_before_row(i));
+    const int r0 = i / group * group;
+    const int rows = min(group, g.tiles_m - r0);
+    u -= wide_units_before_row(r0);
+    const int full = r0 / 2 + 1;
+    int tw;
+    if (u < full * rows) {
+      tw = u / rows;
+      tm = r0 + (u - tw * rows);
+    } else {
+      u -= full * rows;
+      tw = full;
+      int n = rows - 2;
+      while (u >= n && n > 0) { u -= n; n -= 2; ++tw; }
+      tm = 2 * tw + u;
+    }
+    tn = 2 * tw;
     width = tn + 1 <= tm ? 2 : 1;
   } else {
-    // groups of eight row blocks walked column-major, as in decode_tile, so that the units in flight
-    // share few row blocks of either operand
-    constexpr int GROUP = 8;
     const int cols = (g.tiles_n + 1) / 2;
-    const int per_group = GROUP * cols;
+    const int per_group = group * cols;
     const int grp = u / per_group;
     const int in_group = u - grp * per_group;
-    const int rows = min(GROUP, g.tiles_m - grp * GROUP);
+    const int rows = min(group, g.tiles_m - grp * group);
     const int tw = in_group / rows;
-    tm = grp * GROUP + (in_group - tw * rows);
+    tm = grp * group + (in_group - tw * rows);
     tn = 2 * tw;
     width = tn + 1 < g.tiles_n ? 2 : 1;
   }

@@ -32,7 +32,7 @@ thread_local char g_error[512] = "";
 thread_local int g_debug_simt = 0;
 thread_local int g_starve_producers = 0;   // test hook: see bq_produce
 constexpr int WHOLEK_VARIANTS = 3;
-thread_local int g_wholek_variant = 0;   // "wholek_gemm": 0 two streams of 128 x 128 tiles, 1 one CTA per tile, 2 units of 128 x 256
+thread_local int g_wholek_variant = 0;   // "wholek_gemm": 0 units of 128 x 256, 1 two streams of 128 x 128 tiles, 2 one CTA per tile
 // block-quantised GEMMs: 0 = split kernel (tail on its own warps, four-stage ring), 1 = fused tail with a
 // six-stage ring, 2 = fused tail with a four-stage ring; the host-side tuner chooses per shape
 thread_local int g_cta_limit = 0;   // persistent GEMM kernels launch at most this many CTAs (0: one per SM)
@@ -111,6 +111,13 @@ int make_operand_map(CUtensorMap* map, const void* ptr, int esize, int k, int ro
 // ------------------------------------------------------------ GEMM launch
 int sm_count();
 
+// Row blocks per group of the wide-unit order: as many as keep the group's left row blocks
+// (128 rows x k bytes each) within 32 MB of L2; even, 8 to 64.
+int wide_group(long long k_bytes) {
+  const long long fit = (32LL << 20) / std::max<long long>(1, 128 * k_bytes);
+  return int(std::min<long long>(64, std::max<long long>(8, fit))) & ~1;
+}
+
 template <class Epi>
 int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_lo, int batch,
                 int m, int n, int k, int lm, int ln, int sym, unsigned* status,
@@ -128,6 +135,7 @@ int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_
   g.tiles_per_batch = sym ? g.tiles_m * (g.tiles_m + 1) / 2 : g.tiles_m * g.tiles_n;
   g.num_kb = cdiv((long long)k * ES, 128);
   g.debug_simt = g_debug_simt;
+  g.group = wide_group((long long)k * ES);
   g.a_raw = a; g.b_raw = bt; g.status = status;
   long long blocks = (long long)g.tiles_per_batch * batch;
   if (blocks > 0x7fffffffLL) return fail(I8M_E_LIMIT, "%s: too many tiles", name);
@@ -143,7 +151,7 @@ int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_
   }
   // products that accumulate their whole K extent in tensor memory: persistent kernel
   if constexpr (!Epi::BLOCKQ && Epi::PARTS == 1 && Epi::PROMOTE_KB == 0) {
-    if (!g_debug_simt && g_wholek_variant == 2) {
+    if (!g_debug_simt && g_wholek_variant == 0) {
       constexpr size_t WSMEM = wholek_wide_smem_bytes<Epi>();
       auto wk = wholek_wide_kernel<Epi>;
       CUDA_TRY(cudaFuncSetAttribute(wk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(WSMEM)));
@@ -152,7 +160,7 @@ int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_
       LAUNCH_CHECK(name);
       return 0;
     }
-    if (!g_debug_simt && g_wholek_variant == 0) {
+    if (!g_debug_simt && g_wholek_variant == 1) {
       constexpr size_t PSMEM = size_t(WKP_STAGES) * 2 * TILE_BYTES + sizeof(Ctrl) + 1024;
       auto pk = wholek_persistent_kernel<Epi>;
       CUDA_TRY(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PSMEM)));
@@ -201,6 +209,7 @@ int launch_bq(const void* a, const void* bt, int batch, int m, int n, int k, int
   g.tiles_per_batch = sym ? g.tiles_m * (g.tiles_m + 1) / 2 : g.tiles_m * g.tiles_n;
   g.num_kb = cdiv(k, 128);
   g.debug_simt = g_starve_producers ? 0x100 : 0;
+  g.group = 8;
   g.a_raw = a; g.b_raw = bt; g.status = status;
   const long long tiles = (long long)g.tiles_per_batch * batch;
   if (tiles > 0x7fffffffLL / 2) return fail(I8M_E_LIMIT, "%s: too many tiles", name);
@@ -473,13 +482,14 @@ static int float_gemm_to_bq_typed(const void* left, const void* right_t, const F
   g.tiles_per_batch = g.tiles_m * g.tiles_n;
   g.num_kb = cdiv((long long)k * 2, 128);
   g.debug_simt = 0;
+  g.group = wide_group(2LL * k);
   g.a_raw = left; g.b_raw = right_t; g.status = status;
   const long long blocks = (long long)g.tiles_per_batch * batch;
   if (blocks > 0x7fffffffLL) return fail(I8M_E_LIMIT, "float_gemm_to_bq: too many tiles");
   CUtensorMap ma, mb;
   if (int rc = make_operand_map(&ma, left, 2, k, m, batch)) return rc;
   if (int rc = make_operand_map(&mb, right_t, 2, k, n, batch)) return rc;
-  if (g_wholek_variant == 2) {
+  if (g_wholek_variant == 0) {
     constexpr size_t WSMEM = wholek_wide_smem_bytes<Epi>();
     auto wk = wholek_wide_kernel<Epi>;
     CUDA_TRY(cudaFuncSetAttribute(wk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(WSMEM)));

@@ -14,8 +14,9 @@ Differences that a caller can observe:
     only has that flavour for global INT8); the default is the two-pass reduction in a fixed order;
   * the result is a fresh tensor, not a view into the call's workspace;
   * ``tiles`` selects, per product of the global-INT8 route (``aat``, ``square``, ``update``), between this
-    library's two kernels for whole-K products: the reference's tile id 4 (its TMA tile) maps to the
-    persistent TMA kernel (also the default), ids 0-3 (its cp.async tiles) to the one-CTA-per-tile kernel;
+    library's kernels for whole-K products: the reference's tile id 4 (its TMA tile) maps to the
+    persistent kernel with 128 x 256 units (also the default), ids 0-3 (its cp.async tiles) to the
+    one-CTA-per-tile kernel;
     ``autotune`` times the library's kernel variants (``tuning.py``).
 """
 from __future__ import annotations
@@ -160,7 +161,7 @@ class CutlassNSInt8:
             key = (x.device.index, x.dtype, batch, rows, cols, route, compute, steps, bool(fp16_first))
             if route in (native.ROUTE_INT8, native.ROUTE_INT8_FACTORED) and self.tiles:
                 # explicit tiles take precedence over measurements, as in the reference
-                per_op = [0 if self.tiles.get(op, 4) == 4 else 1 for op in ("aat", "square", "update")]
+                per_op = [0 if self.tiles.get(op, 4) == 4 else 2 for op in ("aat", "square", "update")]
                 variant = (per_op[0] << 8) | (per_op[1] << 16) | (per_op[2] << 24)
             elif self._factory.autotune:
                 # per operation first (median of three graph replays, >= 2 % to replace the default), then the

@@ -71,9 +71,11 @@ unsigned long long i8m_launch_count(void);
 int i8m_set_debug_core(int simt);
 /* Kernel variants a host-side tuner can choose between, the counterpart of the tile ids
  * that the reference's KernelFactory times (src/i8muon/_cuda_factory.py:62-102).
- * operation "bq_gemm": 0 = six-stage operand ring (default), 1 = four-stage ring.
- * operation "wholek_gemm" (FP16/BF16/global-INT8 products): 0 = persistent kernel, one CTA per
- * SM (default), 1 = one CTA per output tile.
+ * operation "bq_gemm": 0 = tile tail on its own warpgroup (default), 1 / 2 = fused tail with a
+ * six- / four-stage operand ring.
+ * operation "wholek_gemm" (FP16/BF16/global-INT8 products): 0 = persistent kernel over units of
+ * 128 x 256 (default), 1 = persistent kernel with two streams of 128 x 128 tiles, 2 = one CTA per
+ * output tile.  All variants of an operation give bit-identical results.
  * The choice belongs to the calling thread (two engines on two threads never see each other's)
  * and applies to the stage-level launches that thread makes afterwards; i8m_ns_run takes its own
  * selection as an argument. */

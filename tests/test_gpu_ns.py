@@ -300,7 +300,7 @@ WHOLEK_CASES = [
 
 @pytest.mark.parametrize("route,shape,dtype,precision", WHOLEK_CASES)
 def test_wholek_kernel_variants_agree_bit_for_bit(cuda_device, route, shape, dtype, precision):
-    """The three whole-K kernels (two streams of 128 x 128 tiles, one CTA per tile, 128 x 256 units) accumulate
+    """The three whole-K kernels (128 x 256 units, two streams of 128 x 128 tiles, one CTA per tile) accumulate
     every output element over K in the same order, so whole NS calls agree bit for bit between them."""
     assert native.variant_count("wholek_gemm") == 3
     x = make(shape, dtype, 57, std=1e-3).to(cuda_device)
