@@ -75,9 +75,34 @@ __device__ __forceinline__ void store_user(void* out, int dtype, size_t index, f
   else static_cast<__nv_bfloat16*>(out)[index] = __float2bfloat16_rn(v);
 }
 
+// Packed pairs of 16-bit values: rounding (to nearest even, as round_to) and widening.
+template <typename E>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <typename E>
+__device__ __forceinline__ float2 unpack2(uint32_t v);
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+
 template <typename E, int MODE>
 struct EpiFloat {
   static constexpr bool IS_F32 = sizeof(E) == 4;
+  static constexpr int E_CODE = std::is_same<E, __half>::value ? DT_F16 : (IS_F32 ? DT_F32 : DT_BF16);
   static constexpr int KIND = IS_F32 ? KIND_TF32 : KIND_F16;
   using Elem = E;
   static constexpr int PARTS = IS_F32 ? 2 : 1;
@@ -95,9 +120,100 @@ struct EpiFloat {
   static constexpr uint32_t IDESC = make_idesc(1u, FMT, FMT, TILE, TILE);
   using Args = FloatArgs;
 
+  // Fast path of the 16-bit types for a tile that lies inside the logical extent: packed
+  // conversions, 16-byte loads and stores only, the transposed copy through a 32 x 32 transpose in
+  // the warp's own shared-memory patch (64 contiguous bytes per lane instead of 32 scattered
+  // 2-byte stores).  Same roundings and the same un-fused arithmetic as the general path below.
+  static __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+  static __device__ __forceinline__ bool fast_ok(const GemmGeom& g, const Args& a, const TileCtx& t) {
+    if (t.wsm == nullptr || t.row0 + TILE > g.lm || t.col0 + TILE > g.ln) return false;
+    if constexpr (MODE == MODE_FINAL) {
+      if (a.out_dtype != DT_F16 && a.out_dtype != DT_BF16) return false;
+      return aligned16(a.out) && ((a.transpose ? g.lm : g.ln) & 7) == 0;
+    } else {
+      bool ok = aligned16(a.out) && (g.n & 7) == 0 && (g.m & 7) == 0 && (a.out_t == nullptr || aligned16(a.out_t));
+      if constexpr (MODE == MODE_QUAD) ok = ok && aligned16(a.src) && (g.k & 7) == 0;
+      return ok;
+    }
+  }
+
+  template <class Acc>
+  static __device__ __forceinline__ void run_fast(const GemmGeom& g, const Args& a, const TileCtx& t,
+                                                  const Acc& acc) {
+    const bool diag_tile = g.sym && t.tm == t.tn;
+    const bool mirror = g.sym && t.tm != t.tn;
+    const uint32_t patch = smem_u32(t.wsm);
+#pragma unroll 1
+    for (int c = t.c_begin; c < t.c_end; ++c) {
+      uint32_t v[32];
+      acc.load(c, v);
+      const int colb = t.col0 + c * 32;
+      uint32_t p[16];
+      if constexpr (MODE == MODE_QUAD) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const E*>(a.src) +
+                                                          (size_t(t.b) * g.m + t.row) * g.k + colb);
+        uint32_t rr[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 q = src[i];
+          rr[4 * i] = q.x; rr[4 * i + 1] = q.y; rr[4 * i + 2] = q.z; rr[4 * i + 3] = q.w;
+        }
+        const int dcol = t.tm == t.tn ? t.row - colb : -1;   // this row's diagonal column inside the chunk, if any
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          const float2 r = unpack2<E>(rr[k]);
+          float x0 = __fadd_rn(__fmul_rn(a.cb, r.x), __fmul_rn(a.cc, __uint_as_float(v[2 * k])));
+          float x1 = __fadd_rn(__fmul_rn(a.cb, r.y), __fmul_rn(a.cc, __uint_as_float(v[2 * k + 1])));
+          if (dcol == 2 * k) x0 = __fadd_rn(x0, a.ca);
+          if (dcol == 2 * k + 1) x1 = __fadd_rn(x1, a.ca);
+          p[k] = pack2<E>(x0, x1);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 16; ++k) p[k] = pack2<E>(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
+      }
+      if constexpr (MODE == MODE_FINAL) {
+        // E -> the user's 16-bit type (a second rounding when they differ, as in the general path)
+        if (a.out_dtype != E_CODE) {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const float2 f = unpack2<E>(p[k]);
+            p[k] = a.out_dtype == DT_F16 ? pack2<__half>(f.x, f.y) : pack2<__nv_bfloat16>(f.x, f.y);
+          }
+        }
+        uint16_t* out = static_cast<uint16_t*>(a.out);
+        if (!a.transpose) {
+          store64(out + (size_t(t.b) * g.lm + t.row) * g.ln + colb, p);
+        } else {
+          uint32_t o[16];
+          warp_transpose16(patch, t.lane, p, o);
+          store64(out + (size_t(t.b) * g.ln + colb + t.lane) * g.lm + t.row0 + 32 * t.q, o);
+        }
+      } else {
+        uint16_t* out = static_cast<uint16_t*>(a.out);
+        store64(out + (size_t(t.b) * g.m + t.row) * g.n + colb, p);
+        // transposed copy: the mirrored half of a symmetric product, or the (n x m) transpose
+        // that the next update GEMM consumes (a diagonal tile is bitwise symmetric already)
+        uint16_t* tdst = mirror ? out : static_cast<uint16_t*>(a.out_t);
+        if (tdst != nullptr && !diag_tile) {
+          const int tld = mirror ? g.n : g.m;
+          uint32_t o[16];
+          warp_transpose16(patch, t.lane, p, o);
+          store64(tdst + (size_t(t.b) * (mirror ? g.m : g.n) + colb + t.lane) * tld + t.row0 + 32 * t.q, o);
+        }
+      }
+    }
+  }
+
   template <class Acc>
   static __device__ __forceinline__ void run(const GemmGeom& g, const Args& a, const TileCtx& t,
                                              const Acc& acc) {
+    if constexpr (!IS_F32 && !Acc::IN_REGS) {
+      if (fast_ok(g, a, t)) {   // uniform over the tile's warps
+        run_fast(g, a, t, acc);
+        return;
+      }
+    }
     const bool row_ok = t.row < g.m;
     const bool diag_tile = g.sym && t.tm == t.tn;
     const bool mirror = g.sym && t.tm != t.tn;

@@ -288,7 +288,7 @@ bq_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     t.r = t.q * 32 + lane;
     t.ctrl = ctrl;
     t.diag = ctrl->diag;
-    t.tsm = tsm;
+    t.tsm = tsm; t.wsm = nullptr;
     const int c0 = t.half * CPT;
     const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16) + uint32_t(c0);
     const int mq = g.m / Q, nq = g.n / Q, kq = g.k / Q;

@@ -85,7 +85,13 @@ struct TileCtx {
   float* red;   // shared scratch for the tile-wide reduction (one float per epilogue warp)
   float* diag;  // shared scratch: TILE floats
   uint8_t* tsm; // shared staging tile for transposed stores, or nullptr
+  uint8_t* wsm; // this warp's own WARP_PATCH_BYTES of shared memory (32 x 32 transposes), or nullptr
 };
+
+// A warp's private patch: 32 rows of 64 bytes at a pitch of 80 bytes (16-byte stores of eight
+// consecutive rows and 2-byte loads down a column are both free of bank conflicts).
+constexpr int WARP_PATCH_PITCH = 80;
+constexpr int WARP_PATCH_BYTES = 32 * WARP_PATCH_PITCH;
 
 __device__ __forceinline__ void decode_tile(const GemmGeom& g, int linear, int& b, int& tm,
                                             int& tn) {
@@ -362,7 +368,7 @@ ns_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     t.r = t.q * 32 + lane;
     t.row = row0 + t.r;
     t.ctrl = ctrl;
-    t.red = ctrl->red; t.diag = ctrl->diag; t.tsm = nullptr;
+    t.red = ctrl->red; t.diag = ctrl->diag; t.tsm = nullptr; t.wsm = nullptr;
     t.c_begin = 0; t.c_end = TILE / 32;
     const uint32_t taddr = tmem_base + (uint32_t(t.q * 32) << 16);
     if constexpr (Epi::BLOCKQ) {
@@ -442,6 +448,30 @@ __device__ __forceinline__ void store_row(T* dst, const T (&vals)[32], int count
     for (int j = 0; j < 32; ++j)
       if (j < count) dst[j] = vals[j];
   }
+}
+
+// 32 x 32 transpose of 16-bit values inside a warp.  In: lane r holds row r as 16 packed pairs
+// (columns 2k, 2k + 1 in p[k]).  Out: lane c holds column c as 16 packed pairs (rows 2k, 2k + 1),
+// i.e. 64 contiguous bytes of the transposed matrix.  Goes through the warp's own patch.
+__device__ __forceinline__ void warp_transpose16(uint32_t patch, int lane, const uint32_t (&p)[16], uint32_t (&o)[16]) {
+  const uint32_t mine = patch + uint32_t(lane * WARP_PATCH_PITCH);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) sts128u(mine + 16u * i, make_uint4(p[4 * i], p[4 * i + 1], p[4 * i + 2], p[4 * i + 3]));
+  __syncwarp();
+  const uint32_t col = patch + uint32_t(lane * 2);
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const uint32_t lo = lds16u(col + uint32_t((2 * k) * WARP_PATCH_PITCH));
+    const uint32_t hi = lds16u(col + uint32_t((2 * k + 1) * WARP_PATCH_PITCH));
+    o[k] = lo | (hi << 16);
+  }
+  __syncwarp();   // the patch may be overwritten now
+}
+// 64 contiguous bytes (16-byte aligned) as four vector stores
+__device__ __forceinline__ void store64(void* dst, const uint32_t (&o)[16]) {
+  uint4* d4 = static_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) d4[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
 }
 
 __device__ __forceinline__ float warp_max(float v) {

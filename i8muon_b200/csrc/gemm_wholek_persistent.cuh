@@ -168,7 +168,7 @@ wholek_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     t.ew = warp - 4; t.half = (warp - 4) >> 2;
     t.r = t.q * 32 + lane;
     t.ctrl = ctrl;
-    t.red = ctrl->red; t.diag = ctrl->diag; t.tsm = WholekTileSync<Epi>::value ? tsm : nullptr;
+    t.red = ctrl->red; t.diag = ctrl->diag; t.tsm = WholekTileSync<Epi>::value ? tsm : nullptr; t.wsm = nullptr;
     t.c_begin = t.half * 2; t.c_end = t.half * 2 + 2;
     bool ok = true;
     for (int it = 0; it < my_tiles; ++it) {

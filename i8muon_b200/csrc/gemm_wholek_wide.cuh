@@ -85,7 +85,9 @@ __device__ __forceinline__ void decode_unit(const GemmGeom& g, int units_per_bat
 
 template <class Epi>
 constexpr size_t wholek_wide_smem_bytes() {
-  size_t tail = 0;
+  // after the control block: the staging tile of an epilogue with a tile tail, or one transpose
+  // patch per epilogue warp
+  size_t tail = 8 * WARP_PATCH_BYTES;
   if constexpr (WholekTileSync<Epi>::value) tail = Epi::TSM_BYTES;
   return size_t(WKW_STAGES) * WKW_STAGE_BYTES + sizeof(Ctrl) + tail + 1024;
 }
@@ -221,7 +223,9 @@ wholek_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     t.ew = warp - 4; t.half = (warp - 4) >> 2;
     t.r = t.q * 32 + lane;
     t.ctrl = ctrl;
-    t.red = ctrl->red; t.diag = ctrl->diag; t.tsm = WholekTileSync<Epi>::value ? tsm : nullptr;
+    t.red = ctrl->red; t.diag = ctrl->diag;
+    t.tsm = WholekTileSync<Epi>::value ? tsm : nullptr;
+    t.wsm = WholekTileSync<Epi>::value ? nullptr : tsm + t.ew * WARP_PATCH_BYTES;
     t.c_begin = t.half * 2; t.c_end = t.half * 2 + 2;
     bool ok = true;
     uint32_t tiles_done = 0;

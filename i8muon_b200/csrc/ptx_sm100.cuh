@@ -117,6 +117,11 @@ __device__ __forceinline__ uint32_t lds32u(uint32_t addr) {
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
+__device__ __forceinline__ uint32_t lds16u(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
 // two packed FP32 pairs (four consecutive floats) as one 16-byte store
 __device__ __forceinline__ void sts128_pairs(uint32_t addr, unsigned long long lo, unsigned long long hi) {
   asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(addr), "l"(lo), "l"(hi) : "memory");
