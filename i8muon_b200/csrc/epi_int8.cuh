@@ -48,9 +48,131 @@ struct EpiI8 {
   static constexpr uint32_t IDESC = make_idesc(2u, 1u, 1u, TILE, TILE);  // s32 <- s8 * s8
   using Args = I8Args;
 
+  // Fast path for a tile inside the logical extent: the int8 companion row chunk as two 16-byte
+  // loads, the column diagonal loaded once per chunk (one column per lane) and handed round by
+  // shuffles, 16-byte stores, the transposed final store through the warp's transpose patch.
+  // Every element goes through the same operations, in the same order, as in the general path.
+  static __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+  static __device__ __forceinline__ bool fast_ok(const GemmGeom& g, const Args& a, const TileCtx& t) {
+    if (t.row0 + TILE > g.lm || t.col0 + TILE > g.ln || !aligned16(a.out)) return false;
+    if constexpr (MODE == I8_UPDATE_FINAL) {
+      if (a.out_dtype == DT_F32) { if (a.transpose || (g.ln & 3)) return false; }
+      else if (((a.transpose ? g.lm : g.ln) & 7) || (a.transpose && t.wsm == nullptr)) return false;
+    } else if (g.n & 3) {
+      return false;
+    }
+    if constexpr (MODE == I8_SQUARE) return aligned16(g.a_raw) && (g.k & 15) == 0;
+    if constexpr (MODE == I8_UPDATE || MODE == I8_UPDATE_FINAL) return aligned16(a.row_b) && (g.n & 15) == 0;
+    return true;
+  }
+  static __device__ __forceinline__ float byte_to_float(uint32_t word, int k) {
+    return float(int(int8_t(word >> (8 * k))));
+  }
+  static __device__ __forceinline__ void store128f(float* dst, const float (&r)[32]) {
+    float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) d4[i] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+  }
+
+  template <class Acc>
+  static __device__ __forceinline__ void run_fast(const GemmGeom& g, const Args& a, const TileCtx& t,
+                                                  const Acc& acc) {
+    int imax = 0;
+    float fmax_ = 0.f;
+    float sa = 0.f, sb = 0.f, sq = 0.f, drow = 0.f, xrow = 0.f;
+    if constexpr (MODE != I8_GRAM) {
+      sa = a.a_scale[t.b];
+      drow = a.diag[size_t(t.b) * g.m + t.row];
+    }
+    if constexpr (MODE == I8_SQUARE) {
+      sq = __fmul_rn(__fmul_rn(sa, sa), a.beta);
+      xrow = __fmaf_rn(drow, a.beta, a.alpha);
+    }
+    if constexpr (MODE == I8_UPDATE || MODE == I8_UPDATE_FINAL) {
+      sb = a.b_scale[t.b];
+      if (a.use_gain) sb = __fmul_rn(sb, a.gain);
+    }
+#pragma unroll 1
+    for (int c = t.c_begin; c < t.c_end; ++c) {
+      uint32_t v[32];
+      acc.load(c, v);
+      const int colb = t.col0 + c * 32;
+      const size_t rbase = (size_t(t.b) * g.m + t.row) * g.n + colb;
+      const int dcol = t.row - colb;   // this row's diagonal column inside the chunk when 0 <= dcol < 32
+      if constexpr (MODE == I8_GRAM) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j != dcol) imax = max(imax, abs(int(v[j])));
+        uint4* d4 = reinterpret_cast<uint4*>(static_cast<int*>(a.out) + rbase);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d4[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      } else {
+        const int8_t* comp = (MODE == I8_SQUARE)
+            ? static_cast<const int8_t*>(g.a_raw) + (size_t(t.b) * g.m + t.row) * g.k + colb
+            : a.row_b + rbase;
+        const uint4 c0 = reinterpret_cast<const uint4*>(comp)[0], c1 = reinterpret_cast<const uint4*>(comp)[1];
+        const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        float cj_lane = 0.f;
+        if constexpr (MODE == I8_SQUARE)
+          cj_lane = __fmul_rn(__fmul_rn(a.diag[size_t(t.b) * g.m + colb + t.lane], sa), a.beta);
+        float res[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float accf = float(int(v[j]));
+          const float e = byte_to_float(cw[j >> 2], j & 3);
+          float r;
+          if constexpr (MODE == I8_SQUARE) {
+            const float cj = __shfl_sync(0xffffffffu, cj_lane, j);
+            r = __fmaf_rn(accf, sq, __fmul_rn(e, __fmaf_rn(xrow, sa, cj)));
+            if (j != dcol) fmax_ = fmaxf(fmax_, fabsf(r));
+          } else {
+            r = __fmul_rn(__fmaf_rn(e, drow, __fmul_rn(accf, sa)), sb);
+            if constexpr (MODE == I8_UPDATE) fmax_ = fmaxf(fmax_, fabsf(r));
+          }
+          res[j] = r;
+        }
+        if constexpr (MODE == I8_UPDATE_FINAL) {
+          if (a.out_dtype == DT_F32) {
+            store128f(static_cast<float*>(a.out) + (size_t(t.b) * g.lm + t.row) * g.ln + colb, res);
+          } else {
+            uint32_t p[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+              p[k] = a.out_dtype == DT_F16 ? pack2<__half>(res[2 * k], res[2 * k + 1])
+                                           : pack2<__nv_bfloat16>(res[2 * k], res[2 * k + 1]);
+            uint16_t* out = static_cast<uint16_t*>(a.out);
+            if (!a.transpose) {
+              store64(out + (size_t(t.b) * g.lm + t.row) * g.ln + colb, p);
+            } else {
+              uint32_t o[16];
+              warp_transpose16(smem_u32(t.wsm), t.lane, p, o);
+              store64(out + (size_t(t.b) * g.ln + colb + t.lane) * g.lm + t.row0 + 32 * t.q, o);
+            }
+          }
+        } else {
+          store128f(static_cast<float*>(a.out) + rbase, res);
+        }
+      }
+    }
+    __syncwarp();
+    if constexpr (MODE == I8_GRAM) {
+      imax = warp_max_i(imax);
+      if (t.lane == 0 && imax > 0) atomicMax(static_cast<int*>(a.maximum) + t.b, imax);
+    } else if constexpr (MODE != I8_UPDATE_FINAL) {
+      fmax_ = warp_max(fmax_);
+      if (t.lane == 0 && fmax_ > 0.f) atomic_max_nonneg(static_cast<float*>(a.maximum) + t.b, fmax_);
+    }
+  }
+
   template <class Acc>
   static __device__ __forceinline__ void run(const GemmGeom& g, const Args& a, const TileCtx& t,
                                              const Acc& acc) {
+    if constexpr (!Acc::IN_REGS) {
+      if (fast_ok(g, a, t)) {   // uniform over the tile's warps
+        run_fast(g, a, t, acc);
+        return;
+      }
+    }
     const bool row_ok = t.row < g.m;
     int imax = 0;
     float fmax_ = 0.f;

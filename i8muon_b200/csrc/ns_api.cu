@@ -584,6 +584,18 @@ extern "C" int i8m_symmetric_quant(const void* input, const void* maximum, const
   if (!input || !maximum || !orig_scale || !output || !scale || !diag || batch < 1 || batch > 65535 || m < 1)
     return fail(I8M_E_ARGUMENT, "symmetric_quant: bad argument");
   if (quad && !orig_diag) return fail(I8M_E_ARGUMENT, "symmetric_quant: quad needs the previous diagonal");
+  if (m % 128 == 0 && ((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(output)) & 15u) == 0) {
+    const int t128 = m / 128;
+    dim3 grid128(t128 * (t128 + 1) / 2, batch);
+    if (quad)
+      symmetric_quant128_kernel<float, true><<<grid128, 256, 0, S(stream)>>>(
+          static_cast<const float*>(input), maximum, orig_scale, orig_diag, output, scale, diag, m, c0, c1, c2);
+    else
+      symmetric_quant128_kernel<int, false><<<grid128, 256, 0, S(stream)>>>(
+          static_cast<const int*>(input), maximum, orig_scale, orig_diag, output, scale, diag, m, c0, c1, c2);
+    LAUNCH_CHECK("symmetric_quant");
+    return 0;
+  }
   const int t = cdiv(m, 32);
   dim3 grid(t * (t + 1) / 2, batch);
   if (quad)
@@ -600,6 +612,12 @@ extern "C" int i8m_output_quant(const float* input, const float* maximum, int8_t
                                 float* scale, int batch, int m, int n, i8m_stream_t stream) {
   if (!input || !maximum || !out || !out_t || !scale || batch < 1 || batch > 65535)
     return fail(I8M_E_ARGUMENT, "output_quant: bad argument");
+  if (m % 128 == 0 && n % 128 == 0 &&
+      ((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out_t)) & 15u) == 0) {
+    output_quant128_kernel<<<dim3(n / 128, m / 128, batch), 256, 0, S(stream)>>>(input, maximum, out, out_t, scale, m, n);
+    LAUNCH_CHECK("output_quant");
+    return 0;
+  }
   dim3 grid(cdiv(n, 32), cdiv(m, 32), batch);
   output_quant_kernel<<<grid, 256, 0, S(stream)>>>(input, maximum, out, out_t, scale, m, n);
   LAUNCH_CHECK("output_quant");

@@ -428,6 +428,145 @@ symmetric_quant_kernel(const In* input, const void* maximum, const float* orig_s
   }
 }
 
+// ------------------------------------------- 128 x 128 tiles of int8 codes
+// The two re-quantisers below work on 128 x 128 tiles when the matrix extents are multiples of
+// 128: 16-byte loads of the FP32 / int32 input, the codes of a row chunk packed into one word per
+// lane (128 contiguous bytes per warp store), and the transposed tile written as 16-byte stores
+// after 4 x 4 byte transposes in registers.  Same roundings as the 32 x 32 kernels.
+constexpr int QT_PITCH = 33;   // words per row of the staged tile of codes
+
+__device__ __forceinline__ uint32_t quant4_rn(float4 v, float multiplier) {
+  const uint32_t a = uint8_t(quant_rn(v.x, multiplier)), b = uint8_t(quant_rn(v.y, multiplier));
+  const uint32_t c = uint8_t(quant_rn(v.z, multiplier)), d = uint8_t(quant_rn(v.w, multiplier));
+  return a | (b << 8) | (c << 16) | (d << 24);
+}
+__device__ __forceinline__ float4 load4f(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4f(const int* p) {
+  const int4 v = *reinterpret_cast<const int4*>(p);
+  return make_float4(float(v.x), float(v.y), float(v.z), float(v.w));
+}
+// 4 x 4 byte transpose: w[k] = four consecutive bytes of row k; t[j] = byte j of rows 0..3.
+__device__ __forceinline__ void transpose4x4(const uint32_t (&w)[4], uint32_t (&t)[4]) {
+  const uint32_t x0 = __byte_perm(w[0], w[1], 0x5140), x1 = __byte_perm(w[2], w[3], 0x5140);
+  const uint32_t x2 = __byte_perm(w[0], w[1], 0x7362), x3 = __byte_perm(w[2], w[3], 0x7362);
+  t[0] = __byte_perm(x0, x1, 0x5410); t[1] = __byte_perm(x0, x1, 0x7632);
+  t[2] = __byte_perm(x2, x3, 0x5410); t[3] = __byte_perm(x2, x3, 0x7632);
+}
+// This thread's 16 rows x 4 columns of the staged tile, transposed: tr[j][g] = bytes of column
+// 4 cb + j at rows r0 + 4 g .. r0 + 4 g + 3.  Thread layout of a 256-thread block: warp w covers
+// rows 32 (w >> 1) .. + 31 and word columns 16 (w & 1) .. + 15; lane: rows + 16 (lane >> 4), word
+// column + (lane & 15).  Shared-memory reads are free of bank conflicts at a pitch of 33 words.
+__device__ __forceinline__ void tile_block_transposed(const uint32_t* tile, int r0, int cb, uint32_t (&tr)[4][4]) {
+#pragma unroll
+  for (int gq = 0; gq < 4; ++gq) {
+    uint32_t w[4], t4[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w[k] = tile[(r0 + 4 * gq + k) * QT_PITCH + cb];
+    transpose4x4(w, t4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) tr[j][gq] = t4[j];
+  }
+}
+
+// FP32 (m x n) -> int8 and transposed int8, m and n multiples of 128, 16-byte aligned pointers.
+__global__ void __launch_bounds__(256)
+output_quant128_kernel(const float* input, const float* maximum, int8_t* out, int8_t* out_t, float* scale, int m,
+                       int n) {
+  __shared__ uint32_t tile[128 * QT_PITCH];
+  const int b = blockIdx.z;
+  const float mx = maximum[b];
+  const float multiplier = mx > 0.f ? 127.f / mx : 0.f;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) scale[b] = mx > 0.f ? 1.f / multiplier : 0.f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.y * 128, col0 = blockIdx.x * 128;
+  const float* src = input + (size_t(b) * m + row0) * n + col0 + 4 * lane;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(out + (size_t(b) * m + row0) * n + col0) + lane;
+#pragma unroll 4
+  for (int i = 0; i < 16; ++i) {
+    const int r = warp * 16 + i;
+    const uint32_t q = quant4_rn(load4f(src + size_t(r) * n), multiplier);
+    dst[size_t(r) * (n / 4)] = q;
+    tile[r * QT_PITCH + lane] = q;
+  }
+  __syncthreads();
+  const int r0 = 32 * (warp >> 1) + 16 * (lane >> 4), cb = 16 * (warp & 1) + (lane & 15);
+  uint32_t tr[4][4];
+  tile_block_transposed(tile, r0, cb, tr);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(out_t + (size_t(b) * n + col0 + 4 * cb + j) * m + row0 + r0) =
+        make_uint4(tr[j][0], tr[j][1], tr[j][2], tr[j][3]);
+}
+
+// Lower 128 x 128 tiles of the int32 Gram / FP32 polynomial -> full symmetric int8 matrix with a
+// zero diagonal, the FP32 diagonal and the scale; m a multiple of 128.
+template <typename In, bool QUAD>
+__global__ void __launch_bounds__(256)
+symmetric_quant128_kernel(const In* input, const void* maximum, const float* orig_scale, const float* orig_diag,
+                          int8_t* output, float* scale, float* diag, int m, float c0, float c1, float c2) {
+  __shared__ uint32_t tile[128 * QT_PITCH];
+  const int b = blockIdx.y, pid = blockIdx.x;
+  int tm = int((sqrtf(float(8 * pid + 1)) - 1.f) * 0.5f);
+  while ((tm + 1) * (tm + 2) / 2 <= pid) ++tm;
+  while (tm * (tm + 1) / 2 > pid) --tm;
+  const int tn = pid - tm * (tm + 1) / 2;
+  float mx;
+  if constexpr (QUAD) mx = static_cast<const float*>(maximum)[b];
+  else mx = float(static_cast<const int*>(maximum)[b]);
+  const float multiplier = mx > 0.f ? 127.f / mx : 0.f;
+  const float os = orig_scale[b];
+  const float sa = QUAD ? 1.f : __fmul_rn(os, os);
+  if (pid == 0 && threadIdx.x == 0) scale[b] = mx > 0.f ? sa / multiplier : 0.f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = tm * 128, col0 = tn * 128;
+  const bool diagonal = tm == tn;
+  const In* src = input + (size_t(b) * m + row0) * m + col0 + 4 * lane;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(output + (size_t(b) * m + row0) * m + col0) + lane;
+#pragma unroll 4
+  for (int i = 0; i < 16; ++i) {
+    const int r = warp * 16 + i;
+    const float4 v = load4f(src + size_t(r) * m);
+    uint32_t q = quant4_rn(v, multiplier);
+    if (diagonal) {
+      const int k = r - 4 * lane;   // position of the diagonal element inside this lane's four columns
+      if (k >= 0 && k < 4) {
+        q &= ~(0xffu << (8 * k));
+        const float dv = k == 0 ? v.x : (k == 1 ? v.y : (k == 2 ? v.z : v.w));
+        const size_t di = size_t(b) * m + row0 + r;
+        if constexpr (QUAD) {
+          const float d = orig_diag[di];
+          diag[di] = __fadd_rn(__fmaf_rn(__fmaf_rn(c2, d, c1), d, dv), c0);
+        } else {
+          diag[di] = __fmaf_rn(dv, sa, c0);
+        }
+      }
+    } else {
+      dst[size_t(r) * (m / 4)] = q;
+    }
+    tile[r * QT_PITCH + lane] = q;
+  }
+  __syncthreads();
+  const int r0 = 32 * (warp >> 1) + 16 * (lane >> 4), cb = 16 * (warp & 1) + (lane & 15);
+  uint32_t tr[4][4];
+  tile_block_transposed(tile, r0, cb, tr);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int orow = 4 * cb + j;       // row of the transposed tile, columns r0 .. r0 + 15
+    if (diagonal) {
+      // lower half (column <= row) from the tile itself, upper half from its transpose
+#pragma unroll
+      for (int gq = 0; gq < 4; ++gq) {
+        const int d = orow - (r0 + 4 * gq);
+        const uint32_t keep = d >= 3 ? 0xffffffffu : (d < 0 ? 0u : (1u << (8 * (d + 1))) - 1u);
+        const uint32_t own = tile[orow * QT_PITCH + (r0 >> 2) + gq];
+        tr[j][gq] = (own & keep) | (tr[j][gq] & ~keep);
+      }
+    }
+    *reinterpret_cast<uint4*>(output + (size_t(b) * m + col0 + orow) * m + row0 + r0) =
+        make_uint4(tr[j][0], tr[j][1], tr[j][2], tr[j][3]);
+  }
+}
+
 // R[i][i] <- E(R[i][i] + shift) on every matrix of the batch: the diagonal shift of a
 // completed-square row in the floating first iteration (src/i8muon/_cutlass_prec.py:97-99).
 template <typename E>

@@ -293,6 +293,7 @@ WHOLEK_CASES = [
     ("float", (1, 1500, 640), torch.bfloat16, "float16"),      # tall: transposed final store
     ("gram", (2, 384, 2048), torch.float16, "float16"),
     ("int8", (1, 1100, 1300), torch.bfloat16, None),           # global INT8 with its FP16 first row
+    ("int8", (2, 512, 1024), torch.float32, None),             # every tile interior: the epilogues' fast paths
     ("bq", (1, 1536, 2048), torch.bfloat16, None),             # first row that block-quantises its own result
     ("bq", (1, 2100, 1500), torch.bfloat16, None),
 ]
