@@ -142,7 +142,8 @@ struct EpiFloat {
                                                   const Acc& acc) {
     const bool diag_tile = g.sym && t.tm == t.tn;
     const bool mirror = g.sym && t.tm != t.tn;
-    const uint32_t patch = smem_u32(t.wsm);
+    const WarpPatch wp{smem_u32(t.wsm), t.lane};
+    const int wrow0 = t.row0 + 32 * t.q;   // first row of this warp's block
 #pragma unroll 1
     for (int c = t.c_begin; c < t.c_end; ++c) {
       uint32_t v[32];
@@ -150,14 +151,14 @@ struct EpiFloat {
       const int colb = t.col0 + c * 32;
       uint32_t p[16];
       if constexpr (MODE == MODE_QUAD) {
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const E*>(a.src) +
-                                                          (size_t(t.b) * g.m + t.row) * g.k + colb);
+        // the left operand's block R[wrow0 .. + 31][colb .. + 31]: coalesced into the patch, then one row per lane
+        load_block_rows(wp, reinterpret_cast<const uint8_t*>(static_cast<const E*>(a.src) +
+                                                             (size_t(t.b) * g.m + wrow0) * g.k + colb),
+                        size_t(g.k) * 2);
+        __syncwarp();
         uint32_t rr[16];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4 q = src[i];
-          rr[4 * i] = q.x; rr[4 * i + 1] = q.y; rr[4 * i + 2] = q.z; rr[4 * i + 3] = q.w;
-        }
+        wp.read_own_row(rr);
+        __syncwarp();
         const int dcol = t.tm == t.tn ? t.row - colb : -1;   // this row's diagonal column inside the chunk, if any
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
@@ -181,26 +182,28 @@ struct EpiFloat {
             p[k] = a.out_dtype == DT_F16 ? pack2<__half>(f.x, f.y) : pack2<__nv_bfloat16>(f.x, f.y);
           }
         }
-        uint16_t* out = static_cast<uint16_t*>(a.out);
-        if (!a.transpose) {
-          store64(out + (size_t(t.b) * g.lm + t.row) * g.ln + colb, p);
-        } else {
-          uint32_t o[16];
-          warp_transpose16(patch, t.lane, p, o);
-          store64(out + (size_t(t.b) * g.ln + colb + t.lane) * g.lm + t.row0 + 32 * t.q, o);
-        }
+        wp.write_own_row(p);
+        __syncwarp();
+        uint8_t* out = static_cast<uint8_t*>(a.out);
+        if (!a.transpose)
+          store_block_rows(wp, out + ((size_t(t.b) * g.lm + wrow0) * g.ln + colb) * 2, size_t(g.ln) * 2);
+        else
+          store_block_columns16(wp, out + ((size_t(t.b) * g.ln + colb) * g.lm + wrow0) * 2, size_t(g.lm) * 2);
+        __syncwarp();
       } else {
-        uint16_t* out = static_cast<uint16_t*>(a.out);
-        store64(out + (size_t(t.b) * g.m + t.row) * g.n + colb, p);
+        wp.write_own_row(p);
+        __syncwarp();
+        uint8_t* out = static_cast<uint8_t*>(a.out);
+        store_block_rows(wp, out + ((size_t(t.b) * g.m + wrow0) * g.n + colb) * 2, size_t(g.n) * 2);
         // transposed copy: the mirrored half of a symmetric product, or the (n x m) transpose
         // that the next update GEMM consumes (a diagonal tile is bitwise symmetric already)
-        uint16_t* tdst = mirror ? out : static_cast<uint16_t*>(a.out_t);
+        uint8_t* tdst = mirror ? out : static_cast<uint8_t*>(a.out_t);
         if (tdst != nullptr && !diag_tile) {
           const int tld = mirror ? g.n : g.m;
-          uint32_t o[16];
-          warp_transpose16(patch, t.lane, p, o);
-          store64(tdst + (size_t(t.b) * (mirror ? g.m : g.n) + colb + t.lane) * tld + t.row0 + 32 * t.q, o);
+          store_block_columns16(wp, tdst + ((size_t(t.b) * (mirror ? g.m : g.n) + colb) * tld + wrow0) * 2,
+                                size_t(tld) * 2);
         }
+        __syncwarp();   // the patch is free for the next chunk
       }
     }
   }

@@ -57,7 +57,7 @@ struct EpiI8 {
     if (t.row0 + TILE > g.lm || t.col0 + TILE > g.ln || !aligned16(a.out)) return false;
     if constexpr (MODE == I8_UPDATE_FINAL) {
       if (a.out_dtype == DT_F32) { if (a.transpose || (g.ln & 3)) return false; }
-      else if (((a.transpose ? g.lm : g.ln) & 7) || (a.transpose && t.wsm == nullptr)) return false;
+      else if (((a.transpose ? g.lm : g.ln) & 7) || t.wsm == nullptr) return false;
     } else if (g.n & 3) {
       return false;
     }
@@ -140,14 +140,16 @@ struct EpiI8 {
             for (int k = 0; k < 16; ++k)
               p[k] = a.out_dtype == DT_F16 ? pack2<__half>(res[2 * k], res[2 * k + 1])
                                            : pack2<__nv_bfloat16>(res[2 * k], res[2 * k + 1]);
-            uint16_t* out = static_cast<uint16_t*>(a.out);
-            if (!a.transpose) {
-              store64(out + (size_t(t.b) * g.lm + t.row) * g.ln + colb, p);
-            } else {
-              uint32_t o[16];
-              warp_transpose16(smem_u32(t.wsm), t.lane, p, o);
-              store64(out + (size_t(t.b) * g.ln + colb + t.lane) * g.lm + t.row0 + 32 * t.q, o);
-            }
+            uint8_t* out = static_cast<uint8_t*>(a.out);
+            const WarpPatch wp{smem_u32(t.wsm), t.lane};
+            const int wrow0 = t.row0 + 32 * t.q;
+            wp.write_own_row(p);
+            __syncwarp();
+            if (!a.transpose)
+              store_block_rows(wp, out + ((size_t(t.b) * g.lm + wrow0) * g.ln + colb) * 2, size_t(g.ln) * 2);
+            else
+              store_block_columns16(wp, out + ((size_t(t.b) * g.ln + colb) * g.lm + wrow0) * 2, size_t(g.lm) * 2);
+            __syncwarp();
           }
         } else {
           store128f(static_cast<float*>(a.out) + rbase, res);

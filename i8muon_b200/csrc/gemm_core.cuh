@@ -88,10 +88,10 @@ struct TileCtx {
   uint8_t* wsm; // this warp's own WARP_PATCH_BYTES of shared memory (32 x 32 transposes), or nullptr
 };
 
-// A warp's private patch: 32 rows of 64 bytes at a pitch of 80 bytes (16-byte stores of eight
-// consecutive rows and 2-byte loads down a column are both free of bank conflicts).
-constexpr int WARP_PATCH_PITCH = 80;
-constexpr int WARP_PATCH_BYTES = 32 * WARP_PATCH_PITCH;
+// A warp's private patch of shared memory: 32 rows of 64 bytes, the 16-byte pieces of a row
+// XOR-swizzled with the row number (see WarpPatch) so that the three access patterns of the
+// epilogues are all free of bank conflicts.
+constexpr int WARP_PATCH_BYTES = 32 * 64;
 
 __device__ __forceinline__ void decode_tile(const GemmGeom& g, int linear, int& b, int& tm,
                                             int& tn) {
@@ -450,28 +450,71 @@ __device__ __forceinline__ void store_row(T* dst, const T (&vals)[32], int count
   }
 }
 
-// 32 x 32 transpose of 16-bit values inside a warp.  In: lane r holds row r as 16 packed pairs
-// (columns 2k, 2k + 1 in p[k]).  Out: lane c holds column c as 16 packed pairs (rows 2k, 2k + 1),
-// i.e. 64 contiguous bytes of the transposed matrix.  Goes through the warp's own patch.
-__device__ __forceinline__ void warp_transpose16(uint32_t patch, int lane, const uint32_t (&p)[16], uint32_t (&o)[16]) {
-  const uint32_t mine = patch + uint32_t(lane * WARP_PATCH_PITCH);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) sts128u(mine + 16u * i, make_uint4(p[4 * i], p[4 * i + 1], p[4 * i + 2], p[4 * i + 3]));
-  __syncwarp();
-  const uint32_t col = patch + uint32_t(lane * 2);
-#pragma unroll
-  for (int k = 0; k < 16; ++k) {
-    const uint32_t lo = lds16u(col + uint32_t((2 * k) * WARP_PATCH_PITCH));
-    const uint32_t hi = lds16u(col + uint32_t((2 * k + 1) * WARP_PATCH_PITCH));
-    o[k] = lo | (hi << 16);
+// A 32 x 64-byte block (32 x 32 values of 16 bits, or 32 x 16 of 32 bits) that a warp re-shapes
+// through its patch, so that every global access of an epilogue is coalesced:
+//   own rows      lane r reads / writes row r, four 16-byte pieces (the layout the accumulator
+//                 arrives in: one tile row per lane);
+//   row sweep j   lanes 4 s .. 4 s + 3 hold the four pieces of row 8 j + s: one request covers
+//                 eight rows of 64 contiguous bytes (instead of 32 rows of 16 bytes);
+//   column sweep i (16-bit values) lane (s, a) = (lane >> 2, lane & 3) gathers rows 8 a .. 8 a + 7
+//                 of column 8 i + s: 16 bytes of the transposed block, again eight segments of 64
+//                 contiguous bytes per request.
+// Piece p of row r lives at r * 64 + ((p ^ (r >> 1) ^ (r >> 3)) & 3) * 16.
+struct WarpPatch {
+  uint32_t base;
+  int lane;
+  __device__ __forceinline__ uint32_t piece(int r, int p) const {
+    return base + uint32_t(r * 64 + (((p ^ (r >> 1) ^ (r >> 3)) & 3) << 4));
   }
-  __syncwarp();   // the patch may be overwritten now
-}
-// 64 contiguous bytes (16-byte aligned) as four vector stores
-__device__ __forceinline__ void store64(void* dst, const uint32_t (&o)[16]) {
-  uint4* d4 = static_cast<uint4*>(dst);
+  __device__ __forceinline__ void write_own_row(const uint32_t (&p)[16]) const {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) d4[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) sts128u(piece(lane, i), make_uint4(p[4 * i], p[4 * i + 1], p[4 * i + 2], p[4 * i + 3]));
+  }
+  __device__ __forceinline__ void read_own_row(uint32_t (&p)[16]) const {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = lds128u(piece(lane, i));
+      p[4 * i] = v.x; p[4 * i + 1] = v.y; p[4 * i + 2] = v.z; p[4 * i + 3] = v.w;
+    }
+  }
+  // row sweep: this lane's 16 bytes of request j (row 8 j + (lane >> 2), piece lane & 3)
+  __device__ __forceinline__ int sweep_row(int j) const { return 8 * j + (lane >> 2); }
+  __device__ __forceinline__ uint4 read_sweep(int j) const { return lds128u(piece(sweep_row(j), lane & 3)); }
+  __device__ __forceinline__ void write_sweep(int j, uint4 v) const { sts128u(piece(sweep_row(j), lane & 3), v); }
+  // column sweep of 16-bit values: rows 8 (lane & 3) .. + 7 of column 8 i + (lane >> 2)
+  __device__ __forceinline__ uint4 read_column(int i) const {
+    const int r0 = 8 * (lane & 3);
+    const uint32_t within = uint32_t((lane >> 2) * 2);
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t lo = lds16u(piece(r0 + 2 * k, i) + within);
+      const uint32_t hi = lds16u(piece(r0 + 2 * k + 1, i) + within);
+      w[k] = lo | (hi << 16);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+// Row-major store of a warp's 32 x 64-byte block held one row per lane: through the patch, as four
+// requests of eight 64-byte row segments.  dst = address of the block's first byte, pitch in bytes.
+__device__ __forceinline__ void store_block_rows(const WarpPatch& wp, uint8_t* dst, size_t pitch) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(dst + size_t(wp.sweep_row(j)) * pitch + 16 * (wp.lane & 3)) = wp.read_sweep(j);
+}
+// Transposed store of a block of 16-bit values that sits in the patch: column c of the block
+// becomes 64 contiguous bytes at dst + c * pitch.
+__device__ __forceinline__ void store_block_columns16(const WarpPatch& wp, uint8_t* dst, size_t pitch) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint4*>(dst + size_t(8 * i + (wp.lane >> 2)) * pitch + 16 * (wp.lane & 3)) = wp.read_column(i);
+}
+// Row-major load of a 32 x 64-byte block into the patch (four coalesced requests).
+__device__ __forceinline__ void load_block_rows(const WarpPatch& wp, const uint8_t* src, size_t pitch) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    wp.write_sweep(j, *reinterpret_cast<const uint4*>(src + size_t(wp.sweep_row(j)) * pitch + 16 * (wp.lane & 3)));
 }
 
 __device__ __forceinline__ float warp_max(float v) {
