@@ -48,16 +48,16 @@ struct EpiI8 {
   static constexpr uint32_t IDESC = make_idesc(2u, 1u, 1u, TILE, TILE);  // s32 <- s8 * s8
   using Args = I8Args;
 
-  // Fast path for a tile inside the logical extent: the int8 companion row chunk as two 16-byte
-  // loads, the column diagonal loaded once per chunk (one column per lane) and handed round by
-  // shuffles, 16-byte stores, the transposed final store through the warp's transpose patch.
+  // Fast path for a tile inside the logical extent: every global access of a warp's 32-row block
+  // goes through the warp's shared-memory patch in coalesced requests, the column diagonal is
+  // loaded once per chunk (one column per lane) and handed round by shuffles.
   // Every element goes through the same operations, in the same order, as in the general path.
   static __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
   static __device__ __forceinline__ bool fast_ok(const GemmGeom& g, const Args& a, const TileCtx& t) {
-    if (t.row0 + TILE > g.lm || t.col0 + TILE > g.ln || !aligned16(a.out)) return false;
+    if (t.wsm == nullptr || t.row0 + TILE > g.lm || t.col0 + TILE > g.ln || !aligned16(a.out)) return false;
     if constexpr (MODE == I8_UPDATE_FINAL) {
       if (a.out_dtype == DT_F32) { if (a.transpose || (g.ln & 3)) return false; }
-      else if (((a.transpose ? g.lm : g.ln) & 7) || t.wsm == nullptr) return false;
+      else if ((a.transpose ? g.lm : g.ln) & 7) return false;
     } else if (g.n & 3) {
       return false;
     }
@@ -68,10 +68,20 @@ struct EpiI8 {
   static __device__ __forceinline__ float byte_to_float(uint32_t word, int k) {
     return float(int(int8_t(word >> (8 * k))));
   }
-  static __device__ __forceinline__ void store128f(float* dst, const float (&r)[32]) {
-    float4* d4 = reinterpret_cast<float4*>(dst);
+
+  // 32 columns of 32-bit results per lane row: two halves of 64 bytes through the patch
+  static __device__ __forceinline__ void store_rows32(const WarpPatch& wp, uint8_t* dst, size_t pitch,
+                                                      const uint32_t (&r)[32]) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) d4[i] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    for (int h = 0; h < 2; ++h) {
+      uint32_t half[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) half[k] = r[16 * h + k];
+      wp.write_own_row(half);
+      __syncwarp();
+      store_block_rows(wp, dst + 64 * h, pitch);
+      __syncwarp();
+    }
   }
 
   template <class Acc>
@@ -92,30 +102,34 @@ struct EpiI8 {
       sb = a.b_scale[t.b];
       if (a.use_gain) sb = __fmul_rn(sb, a.gain);
     }
+    const WarpPatch wp{smem_u32(t.wsm), t.lane};
+    const int wrow0 = t.row0 + 32 * t.q;   // first row of this warp's block
 #pragma unroll 1
     for (int c = t.c_begin; c < t.c_end; ++c) {
       uint32_t v[32];
       acc.load(c, v);
       const int colb = t.col0 + c * 32;
-      const size_t rbase = (size_t(t.b) * g.m + t.row) * g.n + colb;
+      const size_t wbase = (size_t(t.b) * g.m + wrow0) * g.n + colb;   // first element of the warp's block
       const int dcol = t.row - colb;   // this row's diagonal column inside the chunk when 0 <= dcol < 32
       if constexpr (MODE == I8_GRAM) {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
           if (j != dcol) imax = max(imax, abs(int(v[j])));
-        uint4* d4 = reinterpret_cast<uint4*>(static_cast<int*>(a.out) + rbase);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) d4[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        store_rows32(wp, reinterpret_cast<uint8_t*>(static_cast<int*>(a.out) + wbase), size_t(g.n) * 4, v);
       } else {
+        // the int8 companion block (g8 for the square, a8 for the update): coalesced into the patch
         const int8_t* comp = (MODE == I8_SQUARE)
-            ? static_cast<const int8_t*>(g.a_raw) + (size_t(t.b) * g.m + t.row) * g.k + colb
-            : a.row_b + rbase;
-        const uint4 c0 = reinterpret_cast<const uint4*>(comp)[0], c1 = reinterpret_cast<const uint4*>(comp)[1];
+            ? static_cast<const int8_t*>(g.a_raw) + (size_t(t.b) * g.m + wrow0) * g.k + colb
+            : a.row_b + wbase;
+        load_block_rows32(wp, reinterpret_cast<const uint8_t*>(comp), size_t(MODE == I8_SQUARE ? g.k : g.n));
+        __syncwarp();
+        const uint4 c0 = lds128u(wp.piece(t.lane, 0)), c1 = lds128u(wp.piece(t.lane, 1));
+        __syncwarp();
         const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         float cj_lane = 0.f;
         if constexpr (MODE == I8_SQUARE)
           cj_lane = __fmul_rn(__fmul_rn(a.diag[size_t(t.b) * g.m + colb + t.lane], sa), a.beta);
-        float res[32];
+        uint32_t res[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const float accf = float(int(v[j]));
@@ -129,20 +143,19 @@ struct EpiI8 {
             r = __fmul_rn(__fmaf_rn(e, drow, __fmul_rn(accf, sa)), sb);
             if constexpr (MODE == I8_UPDATE) fmax_ = fmaxf(fmax_, fabsf(r));
           }
-          res[j] = r;
+          res[j] = __float_as_uint(r);
         }
         if constexpr (MODE == I8_UPDATE_FINAL) {
+          uint8_t* out = static_cast<uint8_t*>(a.out);
           if (a.out_dtype == DT_F32) {
-            store128f(static_cast<float*>(a.out) + (size_t(t.b) * g.lm + t.row) * g.ln + colb, res);
+            store_rows32(wp, out + ((size_t(t.b) * g.lm + wrow0) * g.ln + colb) * 4, size_t(g.ln) * 4, res);
           } else {
             uint32_t p[16];
 #pragma unroll
-            for (int k = 0; k < 16; ++k)
-              p[k] = a.out_dtype == DT_F16 ? pack2<__half>(res[2 * k], res[2 * k + 1])
-                                           : pack2<__nv_bfloat16>(res[2 * k], res[2 * k + 1]);
-            uint8_t* out = static_cast<uint8_t*>(a.out);
-            const WarpPatch wp{smem_u32(t.wsm), t.lane};
-            const int wrow0 = t.row0 + 32 * t.q;
+            for (int k = 0; k < 16; ++k) {
+              const float lo = __uint_as_float(res[2 * k]), hi = __uint_as_float(res[2 * k + 1]);
+              p[k] = a.out_dtype == DT_F16 ? pack2<__half>(lo, hi) : pack2<__nv_bfloat16>(lo, hi);
+            }
             wp.write_own_row(p);
             __syncwarp();
             if (!a.transpose)
@@ -152,7 +165,7 @@ struct EpiI8 {
             __syncwarp();
           }
         } else {
-          store128f(static_cast<float*>(a.out) + rbase, res);
+          store_rows32(wp, reinterpret_cast<uint8_t*>(static_cast<float*>(a.out) + wbase), size_t(g.n) * 4, res);
         }
       }
     }

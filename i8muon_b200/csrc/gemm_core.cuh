@@ -510,6 +510,15 @@ __device__ __forceinline__ void store_block_columns16(const WarpPatch& wp, uint8
   for (int i = 0; i < 4; ++i)
     *reinterpret_cast<uint4*>(dst + size_t(8 * i + (wp.lane >> 2)) * pitch + 16 * (wp.lane & 3)) = wp.read_column(i);
 }
+// Row-major load of a 32 x 32-byte block (int8 companions) into pieces 0 and 1 of the patch rows:
+// two requests of sixteen 32-byte row segments; afterwards lane r finds its row in pieces 0, 1.
+__device__ __forceinline__ void load_block_rows32(const WarpPatch& wp, const uint8_t* src, size_t pitch) {
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int r = 16 * j + (wp.lane >> 1);
+    sts128u(wp.piece(r, wp.lane & 1), *reinterpret_cast<const uint4*>(src + size_t(r) * pitch + 16 * (wp.lane & 1)));
+  }
+}
 // Row-major load of a 32 x 64-byte block into the patch (four coalesced requests).
 __device__ __forceinline__ void load_block_rows(const WarpPatch& wp, const uint8_t* src, size_t pitch) {
 #pragma unroll
