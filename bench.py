@@ -316,9 +316,6 @@ def run_other_config(args):
         if args.reserve_sms > 0:
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.reserve_sms))
         dist.init_process_group("nccl", device_id=dev)
-        if args.reserve_sms > 0:
-            sms = torch.cuda.get_device_properties(dev).multi_processor_count
-            native.call("i8m_set_cta_limit", sms - args.reserve_sms)
     gen = torch.Generator(device=dev).manual_seed(1000)
     coeffs = recommend_coefficients(cfg["steps"], method=cfg["method"])
 
@@ -372,7 +369,8 @@ def run_other_config(args):
         engine = CutlassNSInt8(fp16_first=bool(muon_kw.pop("fp16_first", True)))
         ops = native_step_ops(engine, ns_coefficients=coeffs, **{k: v for k, v in muon_kw.items()})
         plain = [p.data for p in params]
-        stepper = ShardedMuonStep(plain, cfg["steps"], ops, adopt_parameters=bool(args.adopt))
+        stepper = ShardedMuonStep(plain, cfg["steps"], ops, adopt_parameters=bool(args.adopt), gather=args.gather)
+        reserve_sms_if_collective(args, stepper, dev, world)
         buffers = {i: torch.zeros_like(grads[i]) for i in stepper.plan.owned(rank)}
         host = [torch.empty(g.shape, dtype=g.dtype).pin_memory().copy_(g) for g in grads]
 
@@ -603,6 +601,14 @@ def single_kernel(dev, peaks, source, name, b=1):
                            "3xTF32 as BF16 / 6"}
 
 
+def reserve_sms_if_collective(args, stepper, dev, world):
+    """With the collective gather the GEMMs leave `--reserve-sms` SMs to NCCL; peer copies need none."""
+    from i8muon_b200 import native
+    if world > 1 and stepper.gather == "collective" and args.reserve_sms > 0:
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        native.call("i8m_set_cta_limit", sms - args.reserve_sms)
+
+
 def run_native(args):
     import torch.distributed as dist
     from i8muon_b200 import CutlassNSInt8, check_status, native, recommend_coefficients
@@ -622,9 +628,6 @@ def run_native(args):
         if args.reserve_sms > 0:
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.reserve_sms))
         dist.init_process_group("nccl", device_id=dev)
-        if args.reserve_sms > 0:
-            sms = torch.cuda.get_device_properties(dev).multi_processor_count
-            native.call("i8m_set_cta_limit", sms - args.reserve_sms)
 
     shape_list = shapes(args.layers)
     total_flops = ns_flops_of(shape_list)
@@ -636,7 +639,8 @@ def run_native(args):
     params = [(torch.randn(s, device=dev, generator=gen) * 0.02).bfloat16() for s in shape_list]
     grads = [(torch.randn(s, device=dev, generator=gen) * 1e-3).bfloat16() for s in shape_list]
     stepper = ShardedMuonStep(params, NS_STEPS, ops, max_group_bytes=args.group_bytes,
-                              adopt_parameters=bool(args.adopt))
+                              adopt_parameters=bool(args.adopt), gather=args.gather)
+    reserve_sms_if_collective(args, stepper, dev, world)
     buffers = {i: torch.zeros_like(grads[i]) for i in stepper.plan.owned(rank)}
 
     def barrier():
@@ -744,7 +748,8 @@ def run_native(args):
         if phase_table is not None:
             line["phase_ms_max_over_ranks"] = phase_table
         if world > 1:
-            line["config"]["reserve_sms"] = args.reserve_sms
+            line["config"]["gather"] = stepper.gather
+            line["config"]["reserve_sms"] = args.reserve_sms if stepper.gather == "collective" else 0
             line["config"]["adopted_parameters"] = bool(args.adopt)
         if drop_in is not None:
             line["drop_in_api"] = drop_in
@@ -767,8 +772,11 @@ def main():
     parser.add_argument("--fp16-first", type=int, default=1)
     parser.add_argument("--layers", type=int, default=32, help="layers of the parameter set (32 = the full set)")
     parser.add_argument("--group-bytes", type=int, default=2 << 30)
-    parser.add_argument("--reserve-sms", type=int, default=8,
+    parser.add_argument("--reserve-sms", type=int, default=16,
                         help="N > 1: SMs left to the all-gather (the GEMMs launch on the others)")
+    parser.add_argument("--gather", choices=("auto", "copy", "collective"), default="auto",
+                        help="N > 1: how updated parameters reach the other ranks (peer copies over CUDA IPC, "
+                             "or NCCL all-gather on reserved SMs; auto = copies when IPC works)")
     parser.add_argument("--adopt", type=int, default=1,
                         help="N > 1: parameters live in the all-gather buffers and only their owner updates them")
     parser.add_argument("--phases", action="store_true", help="add per-phase device times of one step to the line")

@@ -18,7 +18,7 @@ bookkeeping can be exercised on CPU ranks with stand-in operations.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import inspect
 
@@ -127,10 +127,23 @@ class ShardedMuonStep:
       in-place all-gather delivers every other rank's *updated parameters* straight into this rank's
       parameter storage: no apply pass over foreign parameters, no staging copy.  Every collective of
       a step is in flight under the kernels of the chunks after it; the step waits for them at its end.
+
+    ``gather`` (adopted parameters on CUDA only) chooses what carries the updated parameters:
+
+    * ``"collective"``: ``all_gather_into_tensor`` in place.  NCCL's kernel needs SMs, and the
+      persistent GEMM kernels own every SM they run on, so the caller has to keep some SMs free
+      (``i8m_set_cta_limit`` plus ``NCCL_MAX_CTAS``): the GEMMs lose that share of the GPU.
+    * ``"copy"``: every rank opens the other ranks' flat buffers through CUDA IPC once, and after a
+      chunk's update it *pushes* its own block into each peer's buffer with plain device-to-device
+      copies on a side stream: copy engines over NVLink, no SM, no multicast.  One one-element
+      all-reduce per step, queued behind the pushes on that stream, tells every rank that all
+      blocks addressed to it have landed.
+    * ``"auto"``: ``"copy"`` when the IPC exchange succeeds, else ``"collective"``; ``self.gather``
+      names what is in use.
     """
 
     def __init__(self, params, steps: int, ops: StepOps, group=None, max_group_bytes: int = 2 << 30,
-                 adopt_parameters: bool = False):
+                 adopt_parameters: bool = False, gather: str = "collective"):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -147,8 +160,16 @@ class ShardedMuonStep:
         self._consumed: Dict[int, object] = {}   # chunk -> event: its gradients were read
         self._chunk_list = self._plan_chunks(params)
         self._flat: Dict[int, torch.Tensor] = {}
+        self._peer_flat: Dict[int, List[Optional[torch.Tensor]]] = {}
+        self._push_stream = None
+        self._landed = None
+        if gather not in ("collective", "copy", "auto"):
+            raise ValueError("gather must be 'collective', 'copy' or 'auto'")
+        self.gather = "collective"
         if adopt_parameters and self.world > 1:
             self._adopt(params)
+            if gather != "collective" and params[0].device.type == "cuda":
+                self._open_peer_buffers(required=gather == "copy")
 
     def _plan_chunks(self, like_tensors):
         """(group, first slot, width, staging parity) in the order the step consumes them."""
@@ -171,6 +192,51 @@ class ShardedMuonStep:
                     flat[r * width + j].copy_(params[i])
                     params[i].data = flat[r * width + j]
             self._flat[c] = flat
+
+    def _open_peer_buffers(self, required: bool) -> None:
+        """Exchange CUDA IPC handles of the flat buffers and map every peer's buffers here."""
+        from torch.multiprocessing.reductions import reduce_tensor
+        error = None
+        try:
+            mine = {c: reduce_tensor(flat)[1] for c, flat in self._flat.items()}
+        except Exception as exc:  # the allocator cannot export this memory
+            mine, error = None, exc
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=self.group)
+        peers: Dict[int, List[Optional[torch.Tensor]]] = {c: [None] * self.world for c in self._flat}
+        if all(entry is not None for entry in everyone):
+            from torch.multiprocessing.reductions import rebuild_cuda_tensor
+            try:
+                for r, entry in enumerate(everyone):
+                    if r != self.rank:
+                        for c, handle in entry.items():
+                            peers[c][r] = rebuild_cuda_tensor(*handle)
+            except Exception as exc:
+                error = exc
+        elif error is None:
+            error = RuntimeError("a peer could not export its parameter buffers")
+        # all ranks must agree, or some would wait for pushes that never come
+        verdict = [None] * self.world
+        dist.all_gather_object(verdict, error is None, group=self.group)
+        if all(verdict):
+            self._peer_flat = peers
+            self.gather = "copy"
+            device = next(iter(self._flat.values())).device
+            self._push_stream = torch.cuda.Stream(device=device)
+            self._landed = torch.zeros(1, dtype=torch.int32, device=device)
+        elif required:
+            raise RuntimeError(f"gather='copy' needs CUDA IPC between the ranks of one node: {error}")
+
+    def _push(self, c: int, width: int, count: int) -> None:
+        """Queue the copies of this rank's updated block of chunk c into every peer's flat buffer."""
+        device = self._flat[c].device
+        self._push_stream.wait_stream(torch.cuda.current_stream(device))
+        lo = self.rank * width
+        source = self._flat[c][lo:lo + count]
+        with torch.cuda.stream(self._push_stream):
+            for step in range(1, self.world):
+                r = (self.rank + step) % self.world      # every rank starts with a different peer
+                self._peer_flat[c][r][lo:lo + count].copy_(source, non_blocking=True)
 
     def _buffers_for(self, g: ShardGroup, width: int, like: torch.Tensor, parity: int):
         # two staging sets per signature: chunk n+1 is produced while chunk n is gathered and applied
@@ -286,7 +352,11 @@ class ShardedMuonStep:
                     self.ops.apply([params[i] for i in mine], result)
                     if end is not None:
                         end.record()
-            if self.world > 1:
+            if self.world > 1 and flat is not None and self.gather == "copy":
+                if mine:
+                    self._push(c, width, len(mine))
+                work = None
+            elif self.world > 1:
                 if flat is not None or self._ns_takes_out:
                     source = recv[self.rank * width:(self.rank + 1) * width]
                 else:
@@ -300,6 +370,17 @@ class ShardedMuonStep:
             # apply the previous chunk while this chunk's collective is in flight
             if len(pending) > 1 and not pending[0][6]:
                 self._apply(params, phases, *pending.pop(0)[:6])
+        if self.gather == "copy" and self._flat:
+            # one tiny all-reduce behind this rank's pushes: when it completes here, every rank has
+            # issued it, i.e. every rank's pushes (to this rank too) are complete
+            device = self._landed.device
+            end = self._mark(phases, len(chunks) - 1, "gather_wait", device)
+            self._push_stream.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(self._push_stream):
+                dist.all_reduce(self._landed, group=self.group)
+            torch.cuda.current_stream(device).wait_stream(self._push_stream)
+            if end is not None:
+                end.record()
         while pending:
             entry = pending.pop(0)
             if entry[6]:

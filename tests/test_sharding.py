@@ -243,3 +243,49 @@ def test_sharded_state_dict_loads_into_the_single_device_optimizer():
     again = muon.state_dict()
     assert sorted(again["state"]) == list(range(len(params)))
     assert again["param_groups"][0]["weight_decay_mode"] == "base_lr"
+
+
+def device_problem(dev):
+    params, bufs, grads = make_problem()
+    return ([p.to(dev) for p in params], [b.to(dev) for b in bufs], [[g.to(dev) for g in step] for step in grads])
+
+
+def peer_copy_worker(rank, world, store_path, result_path):
+    dist.init_process_group("gloo", init_method=f"file://{store_path}", rank=rank, world_size=world)
+    try:
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        params, bufs, grads = device_problem(dev)
+        ops = cpu_ops((0.95, 0.9), 0.02, 0.01, "base_lr", "spectral")
+        stepper = ShardedMuonStep(params, steps=5, ops=ops, max_group_bytes=2 * 24 * 40 * 2, adopt_parameters=True,
+                                  gather="copy")
+        assert stepper.gather == "copy" and stepper._push_stream is not None
+        buffers = {i: bufs[i] for i in stepper.plan.owned(rank)}
+        for step_grads in grads:
+            stepper.step(params, step_grads, buffers)
+        torch.cuda.synchronize()
+        torch.save(dict(params=[p.cpu() for p in params]), f"{result_path}.{rank}")
+        dist.barrier()     # nobody unmaps a buffer that a peer may still hold open
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_peer_copy_gather_gives_every_rank_the_unsharded_parameters(cuda_device):
+    """``gather="copy"``: two ranks (two processes sharing the one GPU of the test box, gloo for the
+    control messages) open each other's flat parameter buffers through CUDA IPC and push their updated
+    blocks with device-to-device copies; both end up with the parameters of the unsharded step."""
+    params, bufs, grads = device_problem(cuda_device)
+    ops = cpu_ops((0.95, 0.9), 0.02, 0.01, "base_lr", "spectral")
+    single = ShardedMuonStep(params, steps=5, ops=ops, max_group_bytes=2 * 24 * 40 * 2)
+    buffers = {i: bufs[i] for i in single.plan.owned(0)}
+    for step_grads in grads:
+        single.step(params, step_grads, buffers)
+    want = [p.cpu() for p in params]
+    with tempfile.TemporaryDirectory() as tmp:
+        store, result = os.path.join(tmp, "store"), os.path.join(tmp, "result")
+        mp.spawn(peer_copy_worker, args=(2, store, result), nprocs=2, join=True)
+        for rank in range(2):
+            got = torch.load(f"{result}.{rank}")
+            for p, w in zip(got["params"], want):
+                assert torch.equal(p, w)
