@@ -156,6 +156,7 @@ class ShardedMuonStep:
         keys = [(p.device.type, p.dtype, tuple(p.shape)) for p in params]
         self.plan = build_plan(shapes, keys, self.world, steps)
         self.max_group_bytes = max_group_bytes
+        self.first_chunk_bytes = min(max_group_bytes, 192 << 20)
         self._staging: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._copy_stream = None
         self._ns_takes_out = "out" in inspect.signature(ops.orthogonalise).parameters
@@ -180,8 +181,15 @@ class ShardedMuonStep:
             per_matrix = like.numel() * like.element_size()
             # bound the stacked batch: process the group's slots in column chunks
             chunk = max(1, min(g.width, self.max_group_bytes // max(1, per_matrix)))
-            for first in range(0, g.width, chunk):
-                out.append((g, first, min(chunk, g.width - first), len(out) & 1))
+            first = 0
+            while first < g.width:
+                # the very first chunk of a step has nothing to hide its gradient copy behind (host
+                # gradients are streamed one chunk ahead of the kernels): keep it small
+                width = min(chunk, g.width - first)
+                if not out:
+                    width = max(1, min(width, self.first_chunk_bytes // max(1, per_matrix)))
+                out.append((g, first, width, len(out) & 1))
+                first += width
         return out
 
     def _adopt(self, params, gather: str = "collective") -> None:

@@ -251,10 +251,10 @@ def device_problem(dev):
 
 
 def peer_copy_worker(rank, world, store_path, result_path):
-    dist.init_process_group("gloo", init_method=f"file://{store_path}", rank=rank, world_size=world)
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", init_method=f"file://{store_path}", rank=rank, world_size=world, device_id=dev)
     try:
-        dev = torch.device("cuda", 0)
-        torch.cuda.set_device(dev)
         params, bufs, grads = device_problem(dev)
         ops = cpu_ops((0.95, 0.9), 0.02, 0.01, "base_lr", "spectral")
         stepper = ShardedMuonStep(params, steps=5, ops=ops, max_group_bytes=2 * 24 * 40 * 2, adopt_parameters=True,
@@ -272,9 +272,12 @@ def peer_copy_worker(rank, world, store_path, result_path):
 
 @pytest.mark.gpu
 def test_peer_copy_gather_gives_every_rank_the_unsharded_parameters(cuda_device):
-    """``gather="copy"``: two ranks (two processes sharing the one GPU of the test box, gloo for the
-    control messages) open each other's flat parameter buffers through CUDA IPC and push their updated
-    blocks with device-to-device copies; both end up with the parameters of the unsharded step."""
+    """``gather="copy"``: two ranks on two GPUs map each other's flat parameter buffers (symmetric
+    memory) and push their updated blocks with device-to-device copies; both end up with the parameters
+    of the unsharded step.  Symmetric memory refuses two ranks on one device, so a box with a single
+    GPU skips this."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
     params, bufs, grads = device_problem(cuda_device)
     ops = cpu_ops((0.95, 0.9), 0.02, 0.01, "base_lr", "spectral")
     single = ShardedMuonStep(params, steps=5, ops=ops, max_group_bytes=2 * 24 * 40 * 2)
