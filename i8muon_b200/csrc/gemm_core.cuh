@@ -50,7 +50,7 @@ struct GemmGeom {
   int tiles_per_batch;
   int num_kb;           // K blocks of 128 bytes
   int debug_simt;
-  int group;            // row blocks per group of the wide-unit order (even; set by the launcher)
+  int group;            // row blocks per group of the tile / unit order (even, >= 8; set by the launcher)
   const void* a_raw;    // raw operand pointers (debug core and epilogue reads)
   const void* b_raw;
   unsigned* status;
@@ -104,18 +104,19 @@ __device__ __forceinline__ void decode_tile(const GemmGeom& g, int linear, int& 
     tm = i;
     tn = t - i * (i + 1) / 2;
   } else {
-    // Row blocks are taken in groups of TILE_GROUP and walked column-major inside a group, so
+    // Row blocks are taken in groups and walked column-major inside a group, so
     // that the tiles in flight at one time (one or two per SM, consecutive indices) share few
     // row blocks of both operands: with row-major order the 296 tiles of a wave spanned every
     // column block and the right operand was re-read from DRAM once per 2.6 row blocks
     // (1.4 GB read for 0.27 GB of operands on the 4096 x 14336 FP16 update).
-    constexpr int TILE_GROUP = 8;
-    const int per_group = TILE_GROUP * g.tiles_n;
+    // g.group row blocks per group: as many as keep the group's left row blocks in L2 (at least 8).
+    const int group = g.group;
+    const int per_group = group * g.tiles_n;
     const int grp = t / per_group;
     const int in_group = t - grp * per_group;
-    const int rows = min(TILE_GROUP, g.tiles_m - grp * TILE_GROUP);
+    const int rows = min(group, g.tiles_m - grp * group);
     tn = in_group / rows;
-    tm = grp * TILE_GROUP + (in_group - tn * rows);
+    tm = grp * group + (in_group - tn * rows);
   }
 }
 

@@ -209,7 +209,7 @@ int launch_bq(const void* a, const void* bt, int batch, int m, int n, int k, int
   g.tiles_per_batch = sym ? g.tiles_m * (g.tiles_m + 1) / 2 : g.tiles_m * g.tiles_n;
   g.num_kb = cdiv(k, 128);
   g.debug_simt = g_starve_producers ? 0x100 : 0;
-  g.group = 8;
+  g.group = wide_group(k);
   g.a_raw = a; g.b_raw = bt; g.status = status;
   const long long tiles = (long long)g.tiles_per_batch * batch;
   if (tiles > 0x7fffffffLL / 2) return fail(I8M_E_LIMIT, "%s: too many tiles", name);
