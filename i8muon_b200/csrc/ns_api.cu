@@ -424,8 +424,8 @@ extern "C" int i8m_normalize(const void* x, int in_dtype, const float* norm, voi
                                 static_cast<const In*>(x), norm, static_cast<E*>(a),           \
                                 static_cast<E*>(a_t), static_cast<float*>(a_lo),               \
                                 static_cast<float*>(a_t_lo), rows, cols, lp, hp, transpose, eps)))
-  // 16-bit in and out, rows of whole 16-byte vectors: the vectorised kernel
-  const bool vec = in_dtype != I8M_F32 && compute != I8M_F32 && cols % 8 == 0 && lp % 8 == 0 && hp % 8 == 0 &&
+  // 16-bit out, rows of whole 16-byte vectors: the vectorised kernel
+  const bool vec = compute != I8M_F32 && cols % 8 == 0 && lp % 8 == 0 && hp % 8 == 0 &&
                    ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a) |
                      reinterpret_cast<uintptr_t>(a_t)) & 15u) == 0;
   if (vec) {
@@ -434,7 +434,9 @@ extern "C" int i8m_normalize(const void* x, int in_dtype, const float* norm, voi
   normalize_vec_kernel<In, E><<<vgrid, 256, 0, S(stream)>>>(static_cast<const In*>(x), norm,         \
                                                             static_cast<E*>(a), static_cast<E*>(a_t), \
                                                             rows, cols, lp, hp, transpose, eps)
-    if (in_dtype == I8M_F16 && compute == I8M_F16) NORM_VEC(__half, __half);
+    if (in_dtype == I8M_F32 && compute == I8M_F16) NORM_VEC(float, __half);
+    else if (in_dtype == I8M_F32) NORM_VEC(float, __nv_bfloat16);
+    else if (in_dtype == I8M_F16 && compute == I8M_F16) NORM_VEC(__half, __half);
     else if (in_dtype == I8M_F16) NORM_VEC(__half, __nv_bfloat16);
     else if (compute == I8M_F16) NORM_VEC(__nv_bfloat16, __half);
     else NORM_VEC(__nv_bfloat16, __nv_bfloat16);
@@ -534,6 +536,17 @@ extern "C" int i8m_input_quant(const void* x, int in_dtype, const float* amax, c
   if (!x || !amax || !a8 || !a8_t || !a_scale || !float_dtype_ok(in_dtype) || batch < 1 || batch > 65535)
     return fail(I8M_E_ARGUMENT, "input_quant: bad argument");
   const int prow = transpose ? hp : lp, pcol = transpose ? lp : hp;
+  if (rows == prow && cols == pcol && rows % 128 == 0 && cols % 128 == 0 &&
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a8) | reinterpret_cast<uintptr_t>(a8_t)) & 15u) == 0) {
+    // unpadded input of whole 128 x 128 tiles: vector loads, packed stores, transposes in registers
+    int8_t* same = transpose ? a8_t : a8;
+    int8_t* other = transpose ? a8 : a8_t;
+    DISPATCH_IN(in_dtype, In, (input_quant128_kernel<In><<<dim3(cols / 128, rows / 128, batch), 256, 0, S(stream)>>>(
+                                  static_cast<const In*>(x), amax, norm, same, other, a_scale, rows, cols,
+                                  norm ? eps : 0.f)));
+    LAUNCH_CHECK("input_quant");
+    return 0;
+  }
   dim3 grid(cdiv(pcol, 32), cdiv(prow, 32), batch);
   DISPATCH_IN(in_dtype, In, (input_quant_kernel<In><<<grid, 256, 0, S(stream)>>>(
                                 static_cast<const In*>(x), amax, norm, a8, a8_t, a_scale, rows, cols,

@@ -211,8 +211,18 @@ __device__ __forceinline__ void unpack8(const uint4 raw, float (&v)[8]) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) v[j] = widen<In>(e[j]);
 }
+// eight consecutive input elements (16-byte aligned): one vector load for 16-bit types, two for FP32
+template <typename In>
+__device__ __forceinline__ void load8(const In* p, float (&v)[8]) {
+  if constexpr (sizeof(In) == 4) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    unpack8<In>(*reinterpret_cast<const uint4*>(p), v);
+  }
+}
 
-// 64 x 64 tile of the input per block of 256 threads; In and E are 16-bit types.
+// 64 x 64 tile of the input per block of 256 threads; E is a 16-bit type, In any floating type.
 template <typename In, typename E>
 __global__ void __launch_bounds__(256)
 normalize_vec_kernel(const In* x, const float* norm, E* out, E* out_t, int rows, int cols, int m, int n,
@@ -234,7 +244,7 @@ normalize_vec_kernel(const In* x, const float* norm, E* out, E* out_t, int rows,
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = 0.f;
     if (row < rows && col < cols) {
-      unpack8<In>(*reinterpret_cast<const uint4*>(x + (size_t(b) * rows + row) * cols + col), v);
+      load8<In>(x + (size_t(b) * rows + row) * cols + col, v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(v[j], inv);
     }
@@ -466,6 +476,51 @@ __device__ __forceinline__ void tile_block_transposed(const uint32_t* tile, int 
 #pragma unroll
     for (int j = 0; j < 4; ++j) tr[j][gq] = t4[j];
   }
+}
+
+template <typename In>
+__device__ __forceinline__ float4 load4any(const In* p) {
+  if constexpr (sizeof(In) == 4) {
+    return load4f(p);
+  } else {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const In* e = reinterpret_cast<const In*>(&raw);
+    return make_float4(widen<In>(e[0]), widen<In>(e[1]), widen<In>(e[2]), widen<In>(e[3]));
+  }
+}
+
+// Global-scale quantisation of an unpadded input whose extents are multiples of 128 (the tiles
+// are taken in the input's orientation; `same` has that orientation, `other` is its transpose).
+template <typename In>
+__global__ void __launch_bounds__(256)
+input_quant128_kernel(const In* x, const float* amax, const float* norm, int8_t* same, int8_t* other, float* scale,
+                      int rows, int cols, float eps) {
+  __shared__ uint32_t tile[128 * QT_PITCH];
+  const int b = blockIdx.z;
+  const float mx = amax[b];
+  const float nb = norm ? norm[b] : 1.f;
+  const float multiplier = mx > 0.f ? 127.f / mx : 0.f;
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+    scale[b] = mx > 0.f ? mx / __fmul_rn(127.f, fmaxf(nb, eps)) : 0.f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.y * 128, col0 = blockIdx.x * 128;
+  const In* src = x + (size_t(b) * rows + row0) * cols + col0 + 4 * lane;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(same + (size_t(b) * rows + row0) * cols + col0) + lane;
+#pragma unroll 4
+  for (int i = 0; i < 16; ++i) {
+    const int r = warp * 16 + i;
+    const uint32_t q = quant4_rn(load4any<In>(src + size_t(r) * cols), multiplier);
+    dst[size_t(r) * (cols / 4)] = q;
+    tile[r * QT_PITCH + lane] = q;
+  }
+  __syncthreads();
+  const int r0 = 32 * (warp >> 1) + 16 * (lane >> 4), cb = 16 * (warp & 1) + (lane & 15);
+  uint32_t tr[4][4];
+  tile_block_transposed(tile, r0, cb, tr);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    *reinterpret_cast<uint4*>(other + (size_t(b) * cols + col0 + 4 * cb + j) * rows + row0 + r0) =
+        make_uint4(tr[j][0], tr[j][1], tr[j][2], tr[j][3]);
 }
 
 // FP32 (m x n) -> int8 and transposed int8, m and n multiples of 128, 16-byte aligned pointers.
