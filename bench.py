@@ -153,7 +153,7 @@ def config_dict(world: int, layers: int, precision: str, fp16_first: bool):
     return {"workload": f"llama3-8b-shaped parameter set, {layers} layers x 7 matrices, bf16, "
                         f"precision={precision}, fp16_first={fp16_first}, ns_steps={NS_STEPS} int8_safe",
             "matrices": layers * len(LAYER), "ns_steps": NS_STEPS, "precision": precision,
-            "fp16_first": fp16_first, "parallelism": f"flop-partitioned x{world} + all-gather of updates",
+            "fp16_first": fp16_first, "parallelism": f"flop-partitioned x{world}; updated parameters pushed to the peers (or all-gathered)",
             "l2": "inputs (3 x 14 GB) are larger than L2; no flush needed"}
 
 
@@ -410,7 +410,8 @@ def run_other_config(args):
             "scaling": "strong", "vs_baseline": None, "dtype": cfg["muon"]["precision"], "data": "synthetic",
             "config": {"workload": f"{args.config}: {cfg['what']}", "matrices": len(cfg["shapes"]),
                        "ns_steps": cfg["steps"], "api": "Muon(...).step()" if world == 1 else "ShardedMuonStep",
-                       "cuda_graph": bool(cfg["graph"]) and world == 1, "l2": l2},
+                       "cuda_graph": bool(cfg["graph"]) and world == 1, "l2": l2,
+                       **({"gather": stepper.gather} if world > 1 else {})},
             "algorithmic_flops_per_step": total_flops,
             "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
                          "frac": value / world / peak, "traffic": None,
