@@ -150,7 +150,9 @@ wholek_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       uint32_t wrap = 0;
       int issued = 0;
       bool ok = true;
-      for (int j = 0; j < my_units && ok; ++j) {
+      // test hook (i8m_set_debug_core(2)): issue nothing, so that every consumer's bounded wait runs out
+      const int units = (g.debug_simt & 0x100) ? 0 : my_units;
+      for (int j = 0; j < units && ok; ++j) {
         int b, tm, tn, width;
         decode_unit(g, upb, int(blockIdx.x) + j * int(gridDim.x), b, tm, tn, width);
         const uint32_t bytes = uint32_t(1 + width) * TILE_BYTES;

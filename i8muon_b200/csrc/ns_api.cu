@@ -134,7 +134,7 @@ int launch_gemm(const void* a, const void* a_lo, const void* bt, const void* bt_
   g.sym = sym;
   g.tiles_per_batch = sym ? g.tiles_m * (g.tiles_m + 1) / 2 : g.tiles_m * g.tiles_n;
   g.num_kb = cdiv((long long)k * ES, 128);
-  g.debug_simt = g_debug_simt;
+  g.debug_simt = g_debug_simt | (g_starve_producers ? 0x100 : 0);
   g.group = wide_group((long long)k * ES);
   g.a_raw = a; g.b_raw = bt; g.status = status;
   long long blocks = (long long)g.tiles_per_batch * batch;

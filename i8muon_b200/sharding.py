@@ -157,6 +157,7 @@ class ShardedMuonStep:
         self.plan = build_plan(shapes, keys, self.world, steps)
         self.max_group_bytes = max_group_bytes
         self.first_chunk_bytes = min(max_group_bytes, 192 << 20)
+        self.tail_chunk_bytes = min(max_group_bytes, 128 << 20)
         self._staging: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._copy_stream = None
         self._ns_takes_out = "out" in inspect.signature(ops.orthogonalise).parameters
@@ -176,11 +177,17 @@ class ShardedMuonStep:
     def _plan_chunks(self, like_tensors):
         """(group, first slot, width, staging parity) in the order the step consumes them."""
         out = []
-        for g in self.plan.groups:
+        groups = self.plan.groups
+        for n, g in enumerate(groups):
             like = like_tensors[g.members[0]]
             per_matrix = like.numel() * like.element_size()
             # bound the stacked batch: process the group's slots in column chunks
-            chunk = max(1, min(g.width, self.max_group_bytes // max(1, per_matrix)))
+            budget = self.max_group_bytes
+            if self.world > 1 and n >= len(groups) - 2:
+                # the transfers of the last chunks have little left to hide behind: finer chunks there, so
+                # that a chunk's transfer runs under the kernels of the next chunk of the same group
+                budget = min(budget, self.tail_chunk_bytes)
+            chunk = max(1, min(g.width, budget // max(1, per_matrix)))
             first = 0
             while first < g.width:
                 # the very first chunk of a step has nothing to hide its gradient copy behind (host

@@ -302,6 +302,27 @@ def test_bounded_waits_run_out_and_report_when_the_producer_issues_nothing(cuda_
         native.call("i8m_set_variant", b"bq_gemm", 0)
 
 
+def test_bounded_waits_of_the_whole_k_kernel_run_out_and_report(cuda_device):
+    """The same failure path in the whole-K kernel (128 x 256 units): with the producer issuing nothing, the
+    issuer's wait for operands runs out, the epilogue warps leave at their next poll, tensor memory is freed and
+    the status word holds a timeout code; the next launch on the same context is correct."""
+    dev = cuda_device
+    a = (make_input((1, 128, 256), torch.float32, 9) * 50).half().to(dev)
+    try:
+        want = H.float_gemm(a, a)[0]
+        assert H.status_ok(dev) == 0
+        native.call("i8m_set_debug_core", 2)
+        H.float_gemm(a, a)
+        code = H.status_ok(dev)            # synchronises: about two seconds
+        assert code & 0xf00 in (0x100, 0x200, 0x300) and code != 0
+        native.call("i8m_set_debug_core", 0)
+        again = H.float_gemm(a, a)[0]
+        assert H.status_ok(dev) == 0
+        assert torch.equal(want, again) and torch.isfinite(again).all()
+    finally:
+        native.call("i8m_set_debug_core", 0)
+
+
 # ------------------------------------------------------------------ fused first row of an fp16-first call
 @pytest.mark.parametrize("b,l,h", [(2, 144, 400), (1, 200, 330), (1, 1536, 2048)])
 @pytest.mark.parametrize("user", [torch.bfloat16, torch.float16, torch.float32])
