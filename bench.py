@@ -340,12 +340,16 @@ def run_other_config(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    host_issue = {}
+
     def timed(fn, count):
         barrier()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
+        began = time.perf_counter()
         for _ in range(count):
             fn()
+        host_issue["ms_per_step"] = (time.perf_counter() - began) / count * 1e3   # host time to queue a step
         end.record()
         barrier()
         ms = torch.tensor([start.elapsed_time(end)], device=dev)
@@ -649,12 +653,16 @@ def run_native(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    host_issue = {}
+
     def timed(fn, count):
         barrier()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
+        began = time.perf_counter()
         for _ in range(count):
             fn()
+        host_issue["ms_per_step"] = (time.perf_counter() - began) / count * 1e3   # host time to queue a step
         end.record()
         barrier()
         ms = torch.tensor([start.elapsed_time(end)], device=dev)
@@ -669,6 +677,7 @@ def run_native(args):
     sampler = ClockSampler(local) if rank == 0 else None
     launches_before = native.launch_count()
     seconds = timed(step, args.steps)
+    issue_ms = host_issue["ms_per_step"]
     launches = native.launch_count() - launches_before
     clocks = sampler.stop() if sampler else None
     check_status()
@@ -748,6 +757,7 @@ def run_native(args):
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         if phase_table is not None:
             line["phase_ms_max_over_ranks"] = phase_table
+        line["host_issue_ms_per_step"] = issue_ms
         if world > 1:
             line["config"]["gather"] = stepper.gather
             line["config"]["reserve_sms"] = args.reserve_sms if stepper.gather == "collective" else 0
