@@ -302,6 +302,56 @@ def test_bounded_waits_run_out_and_report_when_the_producer_issues_nothing(cuda_
         native.call("i8m_set_variant", b"bq_gemm", 0)
 
 
+def shifted(t):
+    """The same values at an address that is 4 bytes past a 16-byte boundary: the library then takes its
+    general kernels (32 x 32 tiles, scalar accesses) instead of the vectorised ones."""
+    flat = torch.empty(t.numel() + 4, dtype=t.dtype, device=t.device)
+    view = flat[1:1 + t.numel()].view(t.shape)
+    view.copy_(t)
+    assert view.data_ptr() % 16 != 0
+    return view
+
+
+@pytest.mark.parametrize("b,m,n", [(2, 256, 384), (1, 384, 256), (1, 128, 128)])
+def test_tiled_requantisers_match_the_general_kernels_bit_for_bit(cuda_device, b, m, n):
+    """The 128 x 128-tile kernels of the global-INT8 route (input, symmetric and output quantisers) against the
+    general kernels on the same values: codes, transposed / mirrored codes, scales and diagonals are identical."""
+    dev = cuda_device
+    g = torch.Generator().manual_seed(41)
+    # output quantiser: FP32 (m x n) -> int8, int8^T, scale
+    y = (torch.randn((b, m, n), generator=g) * 3).to(dev)
+    mx = y.abs().amax(dim=(1, 2)).contiguous()
+    fast, slow = H.output_quant(y, mx), H.output_quant(shifted(y), mx)
+    for p, q in zip(fast, slow):
+        assert torch.equal(p, q)
+    # input quantiser: x -> int8, int8^T, scale (with and without the norm in the scale)
+    x = make_input((b, m, n), torch.float32, 42, outliers=True).to(dev)
+    norm, amax = H.stats(x)
+    for nrm in (norm, None):
+        fast, slow = H.input_quant(x, amax, nrm), H.input_quant(shifted(x), amax, nrm)
+        for p, q in zip(fast, slow):
+            assert torch.equal(p, q)
+    # symmetric quantisers: int32 Gram (lower tiles valid) and FP32 polynomial with its diagonal formula
+    gram = torch.randint(-90000, 90000, (b, m, m), generator=g, dtype=torch.int32)
+    gram = torch.tril(gram) + torch.tril(gram, -1).transpose(1, 2)
+    gram = gram.to(dev)
+    off = gram.clone()
+    off.diagonal(dim1=1, dim2=2).zero_()
+    gmax = off.abs().amax(dim=(1, 2)).to(torch.int32).contiguous()
+    scale = torch.rand(b, generator=g).to(dev) * 1e-3 + 1e-4
+    fast, slow = H.symmetric_quant(gram, gmax, scale, None, 0), H.symmetric_quant(shifted(gram), gmax, scale, None, 0)
+    for p, q in zip(fast, slow):
+        assert torch.equal(p, q)
+    poly = torch.tril(torch.randn((b, m, m), generator=g)).to(dev)       # only the lower tiles are read
+    pmax = poly.abs().amax(dim=(1, 2)).contiguous()
+    diag = torch.rand((b, m), generator=g).to(dev)
+    coeffs = (0.7, -1.3, 0.4)
+    fast = H.symmetric_quant(poly, pmax, scale, diag, 1, coeffs)
+    slow = H.symmetric_quant(shifted(poly), pmax, scale, diag, 1, coeffs)
+    for p, q in zip(fast, slow):
+        assert torch.equal(p, q)
+
+
 def test_bounded_waits_of_the_whole_k_kernel_run_out_and_report(cuda_device):
     """The same failure path in the whole-K kernel (128 x 256 units): with the producer issuing nothing, the
     issuer's wait for operands runs out, the epilogue warps leave at their next poll, tensor memory is freed and
