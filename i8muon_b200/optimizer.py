@@ -229,7 +229,6 @@ class Muon(Optimizer):
             if closure is not None:
                 with torch.enable_grad():
                     loss = closure()
-            devices = set()
             for group in self._muon_param_groups:
                 params, grads, bufs = [], [], []
                 for p in group["params"]:
@@ -243,7 +242,6 @@ class Muon(Optimizer):
                     params.append(p)
                     grads.append(p.grad)
                     bufs.append(buf)
-                    devices.add(p.device)
                 muon_step(params, grads, bufs, lr=group["lr"], weight_decay=group["weight_decay"],
                           weight_decay_mode=group["weight_decay_mode"], momentum=group["momentum"],
                           ns_coefficients=group["ns_coefficients"], eps=group["eps"],
@@ -251,8 +249,6 @@ class Muon(Optimizer):
                           ns_engine=self._ns, precision=group["precision"], use_gram=group["use_gram"],
                           use_cuda_graph=self._use_cuda_graph, ns_graphs=self._ns_graphs,
                           gram_aspect_threshold=self._gram_aspect_threshold)
-            for device in devices:
-                post_status(device)
             if self.scalar_optimizer is not None:
                 self.scalar_optimizer.step()
             return loss
@@ -307,6 +303,7 @@ def muon_step(
         ns_graphs = {}
     if not params:
         return
+    raise_if_reported()      # a device-side wait of an earlier step that ran out (no synchronisation)
     lr = _as_float(lr)
     weight_decay = float(weight_decay)
     if weight_decay_mode not in ("absolute", "base_lr", "adjusted_lr"):
@@ -404,6 +401,8 @@ def muon_step(
                             torch.cuda.current_stream().cuda_stream)
                 for original, contiguous in copy_back:
                     original.copy_(contiguous)
+    for device in {g.device for g in grads if g.device.type == "cuda"}:
+        post_status(device)
 
 
 def native_step_ops(ns_engine: CutlassNSInt8, *, lr, weight_decay, momentum, ns_coefficients, eps=EPS,
@@ -452,4 +451,4 @@ def native_step_ops(ns_engine: CutlassNSInt8, *, lr, weight_decay, momentum, ns_
                     native.torch_dtype_code(updates.dtype), mode, decay, -adjusted,
                     torch.cuda.current_stream().cuda_stream)
 
-    return StepOps(momentum=do_momentum, orthogonalise=do_ns, apply=do_apply)
+    return StepOps(momentum=do_momentum, orthogonalise=do_ns, apply=do_apply, begin=raise_if_reported, end=post_status)

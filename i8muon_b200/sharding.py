@@ -106,10 +106,15 @@ class StepOps:
     may return statistics of what it wrote, which are handed to orthogonalise as ``stats=`` if that takes it.
     orthogonalise(x) -> same shape; if it takes ``out=``, the result is written there (the step
     then lets it write straight into the gather buffer and gathers in place).
-    apply(params, updates): updates is (len(params), *shape)."""
+    apply(params, updates): updates is (len(params), *shape).
+    begin() / end(device), optional: called when a step starts / after its last kernel is queued (the
+    native operations use them to surface a device-side wait that ran out: end queues a copy of the status
+    word, the next begin raises if it arrived non-zero; neither synchronises)."""
     momentum: Callable
     orthogonalise: Callable
     apply: Callable
+    begin: Optional[Callable] = None
+    end: Optional[Callable] = None
 
 
 class ShardedMuonStep:
@@ -332,6 +337,8 @@ class ShardedMuonStep:
         stream, chunk by chunk, overlapped with the kernels of the chunks before them.
         ``phases``: a list that receives (chunk, phase, start event, end event) for every phase."""
         chunks = self._chunk_list
+        if self.ops.begin is not None:
+            self.ops.begin()
         ready = self._stream_gradients(chunks, grads, host_grads) if host_grads is not None else None
         pending = []
         for c, (g, first, width, parity) in enumerate(chunks):
@@ -416,6 +423,8 @@ class ShardedMuonStep:
                         end.record()
             else:
                 self._apply(params, phases, *entry[:6])
+        if self.ops.end is not None and chunks:
+            self.ops.end(grads[chunks[0][0].members[0]].device)
 
     def _apply(self, params, phases, c: int, g: ShardGroup, first: int, width: int, recv, work) -> None:
         device = recv.device
