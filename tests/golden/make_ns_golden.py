@@ -156,4 +156,4 @@ def main(out_dir: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/ns_golden")
+    main(sys.argv[1] if len(sys.argv) > 1 else "ns_golden_out")
