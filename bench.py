@@ -567,6 +567,53 @@ def single_kernel(dev, peaks, source, name, b=1):
         flops = 2.0 * lp * lp * hp * b
         peak, sustained = 2.0 * peaks["bf16_tflops"], 2.0 * peaks["bf16_tflops_sustained"]
         kernel = f"whole-K kernel<EpiI8<update>> B={b} 4096x4096 (k=4096), FP32 result + maximum"
+    elif name in ("i8_gram", "i8_square"):
+        lp = 4096
+        a8 = rand_i8(b, lp, lp)
+        if name == "i8_gram":
+            out, mx = torch.empty((b, lp, lp), device=dev, dtype=torch.int32), torch.zeros(b, device=dev, dtype=torch.int32)
+
+            def launch():
+                native.call("i8m_i8_gemm", 0, a8.data_ptr(), a8.data_ptr(), None, out.data_ptr(), mx.data_ptr(), None,
+                            None, None, b, lp, lp, lp, lp, lp, 0.0, 0.0, 0, 0, 0, status, stream)
+        else:
+            gs, dg = rand_f(b), rand_f(b, lp, lo=0.5, span=0.5)
+            out, mx = torch.empty((b, lp, lp), device=dev), torch.zeros(b, device=dev)
+
+            def launch():
+                native.call("i8m_i8_gemm", 1, a8.data_ptr(), a8.data_ptr(), None, out.data_ptr(), mx.data_ptr(),
+                            gs.data_ptr(), None, dg.data_ptr(), b, lp, lp, lp, lp, lp, -4.0, 2.0, 0, 0, 0, status, stream)
+        tiles = (lp // 128) * (lp // 128 + 1) // 2
+        flops = 2.0 * 128 * 128 * tiles * lp * b
+        peak, sustained = 2.0 * peaks["bf16_tflops"], 2.0 * peaks["bf16_tflops_sustained"]
+        kernel = f"wholek_wide_kernel<EpiI8<{'gram' if name == 'i8_gram' else 'square'}>> B={b} 4096x4096 lower tiles (k=4096)"
+    elif name == "bq_final":
+        lp, hp = 4096, 14336
+        pq, at, a8 = rand_i8(b, lp, lp), rand_i8(b, hp, lp), rand_i8(b, lp, hp)
+        sp, sa = rand_f(b, lp // 128, lp // 128), rand_f(b, lp // 128, hp // 128)
+        dp = rand_f(b, lp, lo=0.5, span=0.5)
+        out = torch.empty((b, hp, lp), device=dev, dtype=torch.bfloat16)
+
+        def launch():
+            native.call("i8m_bq_gemm", 0, 2, pq.data_ptr(), sp.data_ptr(), dp.data_ptr(), at.data_ptr(), sa.data_ptr(),
+                        a8.data_ptr(), out.data_ptr(), None, None, None, b, lp, hp, lp, lp, hp, 0.0, 0.0, 0.0, 1, 1,
+                        native.BF16, status, stream)
+        flops = 2.0 * lp * lp * hp * b
+        peak, sustained = 2.0 * peaks["bf16_tflops"], 2.0 * peaks["bf16_tflops_sustained"]
+        kernel = f"bq_split_kernel<EpiBq<int8, final update>> B={b} 4096x14336 (k=4096), transposed bf16 result"
+    elif name == "float_to_bq":
+        lp, hp = 4096, 14336
+        q = (torch.randn((b, lp, lp), device=dev, generator=gen) * 0.05).half()
+        at = (torch.randn((b, hp, lp), device=dev, generator=gen) * 0.05).half()
+        codes, codes_t = torch.empty((b, lp, hp), device=dev, dtype=torch.uint8), torch.empty((b, hp, lp), device=dev, dtype=torch.uint8)
+        scale = torch.empty((b, lp // 128, hp // 128), device=dev)
+
+        def launch():
+            native.call("i8m_float_gemm_to_bq", q.data_ptr(), at.data_ptr(), codes.data_ptr(), codes_t.data_ptr(),
+                        scale.data_ptr(), native.F16, native.BF16, b, lp, hp, lp, lp, hp, lp, hp, status, stream)
+        flops = 2.0 * lp * lp * hp * b
+        peak, sustained = peaks["bf16_tflops"], peaks["bf16_tflops_sustained"]
+        kernel = f"wholek_wide_kernel<EpiFloatToBq<half>> B={b} 4096x14336 (k=4096), INT8 codes of A and A^T + block scales"
     elif name == "fp32_gram":
         lp, hp = 1024, 4096
         x = torch.randn((b, lp, hp), device=dev, generator=gen) * 0.02
@@ -802,7 +849,7 @@ def main():
     parser.add_argument("--wholek-variant", type=int, default=0,
                         help="with --only-fp16: whole-K kernel (0 units of 128x256, 1 two streams of 128x128 tiles, "
                              "2 one CTA per tile)")
-    parser.add_argument("--only-kernel", choices=("bq_gram", "bq_poly", "i8_update", "fp32_gram"), default=None,
+    parser.add_argument("--only-kernel", choices=("bq_gram", "bq_poly", "bq_final", "float_to_bq", "i8_gram", "i8_square", "i8_update", "fp32_gram"), default=None,
                         help="only time this GEMM kernel alone (small case for ncu); --kernel-batch matrices")
     parser.add_argument("--kernel-batch", type=int, default=1)
     args = parser.parse_args()
