@@ -205,29 +205,40 @@ class ShardedMuonStep:
         return out
 
     def _adopt(self, params, gather: str = "collective") -> None:
-        symm = None
+        symm, failure_to_import = None, None
         if gather != "collective" and params[0].device.type == "cuda":
             # plain peer mappings only: no multicast object is ever bound to these buffers
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             try:
                 import torch.distributed._symmetric_memory as symm
-            except Exception as exc:
-                if gather == "copy":
-                    raise RuntimeError(f"gather='copy' needs torch symmetric memory: {exc}") from exc
+            except Exception as exc:       # agreed on with the other ranks below
+                failure_to_import = exc
+                symm = None
+        failure = failure_to_import
         for c, (g, first, width, _) in enumerate(self._chunk_list):
             like = params[g.members[0]]
             shape = (self.world * width, *like.shape)
-            if symm is not None:
-                flat = symm.empty(shape, dtype=like.dtype, device=like.device).zero_()
-            else:
+            flat = None
+            if symm is not None and failure is None:
+                try:
+                    flat = symm.empty(shape, dtype=like.dtype, device=like.device).zero_()
+                except Exception as exc:       # this rank cannot allocate symmetric memory: ordinary buffers
+                    failure = exc
+            if flat is None:
                 flat = torch.zeros(shape, dtype=like.dtype, device=like.device)
             for r in range(self.world):
                 for j, i in enumerate(g.slots[r][first:first + width]):
                     flat[r * width + j].copy_(params[i])
                     params[i].data = flat[r * width + j]
             self._flat[c] = flat
-        if symm is not None:
-            self._open_peer_buffers(symm, required=gather == "copy")
+        if gather != "collective" and params[0].device.type == "cuda":
+            # the rendezvous is collective: enter it only if every rank holds symmetric buffers
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, symm is not None and failure is None, group=self.group)
+            if all(everyone):
+                self._open_peer_buffers(symm, required=gather == "copy")
+            elif gather == "copy":
+                raise RuntimeError(f"gather='copy' needs torch symmetric memory on every rank: {failure}")
 
     def _open_peer_buffers(self, symm, required: bool) -> None:
         """Map every peer's flat buffers here (one rendezvous per buffer, same order on every rank)."""
