@@ -27,6 +27,7 @@ struct FloatArgs {
   int out_dtype;    // MODE_FINAL: DType of the user tensor
   int transpose;    // MODE_FINAL: store (ln x lm)
   float ca, cb, cc;
+  float* amax;      // MODE_FINAL, optional: [batch] maximum magnitude of the stored values (zeroed by the caller)
 };
 
 template <typename E>
@@ -144,6 +145,7 @@ struct EpiFloat {
     const bool mirror = g.sym && t.tm != t.tn;
     const WarpPatch wp{smem_u32(t.wsm), t.lane};
     const int wrow0 = t.row0 + 32 * t.q;   // first row of this warp's block
+    float stored_max = 0.f;
 #pragma unroll 1
     for (int c = t.c_begin; c < t.c_end; ++c) {
       uint32_t v[32];
@@ -182,6 +184,13 @@ struct EpiFloat {
             p[k] = a.out_dtype == DT_F16 ? pack2<__half>(f.x, f.y) : pack2<__nv_bfloat16>(f.x, f.y);
           }
         }
+        if (a.amax != nullptr) {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const float2 f = a.out_dtype == DT_F16 ? unpack2<__half>(p[k]) : unpack2<__nv_bfloat16>(p[k]);
+            stored_max = fmaxf(stored_max, fmaxf(fabsf(f.x), fabsf(f.y)));
+          }
+        }
         wp.write_own_row(p);
         __syncwarp();
         uint8_t* out = static_cast<uint8_t*>(a.out);
@@ -206,6 +215,12 @@ struct EpiFloat {
         __syncwarp();   // the patch is free for the next chunk
       }
     }
+    if constexpr (MODE == MODE_FINAL) {
+      if (a.amax != nullptr) {
+        stored_max = warp_max(stored_max);
+        if (t.lane == 0 && stored_max > 0.f) atomic_max_nonneg(a.amax + t.b, stored_max);
+      }
+    }
   }
 
   template <class Acc>
@@ -220,6 +235,7 @@ struct EpiFloat {
     const bool row_ok = t.row < g.m;
     const bool diag_tile = g.sym && t.tm == t.tn;
     const bool mirror = g.sym && t.tm != t.tn;
+    float stored_max = 0.f;
     auto body = [&](const int c) {
       uint32_t v[32];
       acc.load(c, v);
@@ -246,6 +262,18 @@ struct EpiFloat {
       if (!row_ok) return;
       const int ncol = min(32, g.n - colb);
       if constexpr (MODE == MODE_FINAL) {
+        if (a.amax != nullptr && t.row < g.lm) {
+          // the value as the user's tensor holds it
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (colb + j < g.ln) {
+              const float held = a.out_dtype == DT_F32 ? val[j]
+                                 : a.out_dtype == DT_F16 ? __half2float(__float2half_rn(val[j]))
+                                                         : __bfloat162float(__float2bfloat16_rn(val[j]));
+              stored_max = fmaxf(stored_max, fabsf(held));
+            }
+          }
+        }
         // a thread's 32 consecutive outputs leave as 16-byte stores when the row is aligned
         const size_t fbase = (size_t(t.b) * g.lm + t.row) * g.ln + colb;
         const int esz = a.out_dtype == DT_F32 ? 4 : 2;
@@ -337,6 +365,13 @@ struct EpiFloat {
     } else {
 #pragma unroll 1
       for (int c = t.c_begin; c < t.c_end; ++c) body(c);
+    }
+    if constexpr (MODE == MODE_FINAL) {
+      if (a.amax != nullptr) {
+        __syncwarp();
+        stored_max = warp_max(stored_max);
+        if (t.lane == 0 && stored_max > 0.f) atomic_max_nonneg(a.amax + t.b, stored_max);
+      }
     }
   }
 };

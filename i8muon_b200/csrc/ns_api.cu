@@ -31,6 +31,7 @@ thread_local char g_error[512] = "";
 // selection as an argument and restores the thread's own setting when it returns.
 thread_local int g_debug_simt = 0;
 thread_local int g_starve_producers = 0;   // test hook: see bq_produce
+thread_local float* g_final_amax = nullptr;  // set by run_float around its final product: [batch] maximum of the stored result
 constexpr int WHOLEK_VARIANTS = 3;
 thread_local int g_wholek_variant = 0;   // "wholek_gemm": 0 units of 128 x 256, 1 two streams of 128 x 128 tiles, 2 one CTA per tile
 // block-quantised GEMMs: 0 = split kernel (tail on its own warps, four-stage ring), 1 = fused tail with a
@@ -253,6 +254,7 @@ int float_gemm_typed(const void* left, const void* left_lo, const void* right_t,
   a.src = left; a.src_lo = left_lo;
   a.out_dtype = out_dtype; a.transpose = transpose;
   a.ca = ca; a.cb = cb; a.cc = cc;
+  a.amax = final ? g_final_amax : nullptr;
   if (mode == 1) {
     if (final) return fail(I8M_E_ARGUMENT, "float_gemm: the polynomial mode has no final variant");
     if (k != n) return fail(I8M_E_ARGUMENT, "float_gemm: polynomial mode needs a square left operand");
@@ -889,7 +891,7 @@ struct BqOperands {   // where a floating first row leaves its result for the bl
 
 int run_float(const NsCall& c, Bump& ws, bool plan, bool gram, const void* x, void* out,
               int out_dtype, int steps, const double* coeffs, int compute, bool normalize_input,
-              bool factored = false, const BqOperands* to_bq = nullptr) {
+              bool factored = false, const BqOperands* to_bq = nullptr, float* final_amax = nullptr) {
   const int B = c.batch, rows = c.rows, cols = c.cols;
   const int l = std::min(rows, cols), h = std::max(rows, cols);
   const int lp = pad_to(l, 16), hp = pad_to(h, 16);
@@ -914,6 +916,10 @@ int run_float(const NsCall& c, Bump& ws, bool plan, bool gram, const void* x, vo
   auto gemm = [&](const FMat& left, const FMat& right, const FMat& o, const FMat& ot, int mode, int n,
                   int k, int ln, int sym, int final, int tr, void* user, double ca, double cb,
                   double cc) -> int {
+    // the final product can leave the maximum magnitude of what it stores (the global-INT8 rows that
+    // follow an FP16 first row quantise it with that scale: no statistics pass over the result)
+    struct Handover { ~Handover() { g_final_amax = nullptr; } } reset;
+    g_final_amax = final ? final_amax : nullptr;
     return i8m_float_gemm(left.p, left.lo, right.p, right.lo, final ? user : o.p, ot.p, o.lo, ot.lo,
                           compute, mode, B, lp, n, k, l, ln, sym, final, tr, out_dtype, float(ca),
                           float(cb), float(cc), c.status, c.stream);
@@ -984,7 +990,7 @@ int run_float(const NsCall& c, Bump& ws, bool plan, bool gram, const void* x, vo
 
 // global-scale INT8 NS (src/i8muon/_cutlass.py:162-251)
 int run_int8(const NsCall& c, Bump& ws, bool plan, const void* x, int steps, const double* coeffs,
-             bool normalize_input, bool factored = false) {
+             bool normalize_input, bool factored = false, const float* given_amax = nullptr) {
   const int B = c.batch, rows = c.rows, cols = c.cols;
   const int l = std::min(rows, cols), h = std::max(rows, cols);
   const int lp = pad_to(l, 16), hp = pad_to(h, 16);
@@ -1009,9 +1015,11 @@ int run_int8(const NsCall& c, Bump& ws, bool plan, const void* x, int steps, con
     return fail(I8M_E_LIMIT, "inner dimension can overflow the int32 accumulator");
 
   CUDA_TRY(cudaMemsetAsync(maxima, 0, size_t(3) * steps * B * sizeof(float), c.stream));
-  if (int rc = call_stats(c, x, B, (long long)rows * cols, scratch, sbytes, normalize_input ? norm : nullptr, amax))
-    return rc;
-  if (int rc = i8m_input_quant(x, c.dtype, amax, normalize_input ? norm : nullptr, a8, a8t, a_scale, B,
+  if (given_amax == nullptr) {
+    if (int rc = call_stats(c, x, B, (long long)rows * cols, scratch, sbytes, normalize_input ? norm : nullptr, amax))
+      return rc;
+  }
+  if (int rc = i8m_input_quant(x, c.dtype, given_amax ? given_amax : amax, normalize_input ? norm : nullptr, a8, a8t, a_scale, B,
                                rows, cols, lp, hp, transpose, c.eps, c.stream))
     return rc;
   for (int it = 0; it < steps; ++it) {
@@ -1226,12 +1234,18 @@ int ns_dispatch(const NsCall& c, Bump& ws, bool plan) {
         return rc;
       }
       void* first = ws.take(size_t(c.batch) * c.rows * c.cols * dtype_size(c.dtype));
+      // global INT8: the first row's final store also leaves max |X1| per matrix, the scale of the rows
+      // that follow (deterministic: a maximum does not depend on the order of its operands)
+      float* first_amax = bq ? nullptr : ws.take_n<float>(c.batch);
       size_t mark = ws.used;
-      if (int rc = run_float(c, ws, plan, false, c.x, first, c.dtype, 1, c.coeffs, I8M_F16, true)) return rc;
+      if (!plan && first_amax) CUDA_TRY(cudaMemsetAsync(first_amax, 0, size_t(c.batch) * sizeof(float), c.stream));
+      if (int rc = run_float(c, ws, plan, false, c.x, first, c.dtype, 1, c.coeffs, I8M_F16, true, false, nullptr,
+                             first_amax))
+        return rc;
       size_t after_float = ws.used;
       ws.used = mark;  // the quantised stage reuses the floating stage's scratch
       int rc = bq ? run_bq(c, ws, plan, false, first, c.steps - 1, plan ? nullptr : c.coeffs + 3, false)
-                  : run_int8(c, ws, plan, first, c.steps - 1, plan ? nullptr : c.coeffs + 3, false);
+                  : run_int8(c, ws, plan, first, c.steps - 1, plan ? nullptr : c.coeffs + 3, false, false, first_amax);
       ws.used = std::max(ws.used, after_float);
       return rc;
     }
