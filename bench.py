@@ -471,8 +471,8 @@ def dominant_kernel_roofline(dev, peaks, source, b=4):
     sustained = 2.0 * peaks["bf16_tflops_sustained"]
     return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
             "frac_of_sustained_peak": achieved / sustained, "peak_sustained": sustained,
-            "traffic": 377.0e6 * b, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one B=1 "
-            "launch (283.5 + 93.5 MB), scaled by the batch: every batch matrix is an independent set of tiles",
+            "traffic": 222.5e6 * b, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one B=1 "
+            "launch (134.6 + 87.9 MB), scaled by the batch: every batch matrix is an independent set of tiles",
             "kernel": f"bq_split_kernel<EpiBq<int8, update>> B={b} 4096x14336 (k=4096)",
             "flops_per_launch": flops, "ms_per_launch": seconds * 1e3,
             "peak_source": f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({source}); there is no measured INT8 "
