@@ -292,3 +292,34 @@ def test_peer_copy_gather_gives_every_rank_the_unsharded_parameters(cuda_device)
             got = torch.load(f"{result}.{rank}")
             for p, w in zip(got["params"], want):
                 assert torch.equal(p, w)
+
+
+def test_chunk_plan_keeps_the_first_chunk_small_and_the_tail_fine():
+    """The step consumes shape groups in chunks: the very first chunk is at most ``first_chunk_bytes`` (nothing hides
+    its gradient copy), and with more than one rank the last two groups are cut to ``tail_chunk_bytes`` (a chunk's
+    transfer to the peers runs under the next chunk of the same group).  Every slot is covered exactly once."""
+    shapes = LLAMA_LAYER * 32
+    params = [torch.empty(s, dtype=torch.bfloat16, device="meta") for s in shapes]
+    ops = cpu_ops((0.95, 0.9), 0.02, 0.01, "base_lr", "spectral")
+    stepper = ShardedMuonStep(params, steps=5, ops=ops)          # one rank
+    chunks = stepper._chunk_list
+    first_group, _, first_width, _ = chunks[0]
+    assert first_width * 14336 * 4096 * 2 <= stepper.first_chunk_bytes and first_width >= 1
+    for g in stepper.plan.groups:
+        covered = sorted((first, width) for grp, first, width, _ in chunks if grp is g)
+        assert covered[0][0] == 0 and sum(w for _, w in covered) == g.width
+        assert all(a + w == b for (a, w), (b, _) in zip(covered, covered[1:]))
+    # eight ranks: same plan code, the rank count only enters through the partition and the tail rule
+    keys = [("cuda", torch.bfloat16, s) for s in shapes]
+    stepper.world = 8
+    stepper.plan = build_plan(shapes, keys, 8, 5)
+    chunks = stepper._plan_chunks(params)
+    tail_groups = stepper.plan.groups[-2:]
+    for grp, first, width, _ in chunks:
+        numel = 1
+        for d in shapes[grp.members[0]]:
+            numel *= d
+        if any(grp is t for t in tail_groups):
+            assert width * numel * 2 <= stepper.tail_chunk_bytes or width == 1
+    assert [parity for *_, parity in chunks] == [i & 1 for i in range(len(chunks))]
+    assert len([c for c in chunks if any(c[0] is t for t in tail_groups)]) >= 3   # q/o in three chunks + k/v
