@@ -93,8 +93,8 @@ struct TileCtx {
 // epilogues are all free of bank conflicts.
 constexpr int WARP_PATCH_BYTES = 32 * 64;
 
-__device__ __forceinline__ void decode_tile(const GemmGeom& g, int linear, int& b, int& tm,
-                                            int& tn) {
+__host__ __device__ __forceinline__ void decode_tile(const GemmGeom& g, int linear, int& b, int& tm,
+                                                     int& tn) {
   b = linear / g.tiles_per_batch;
   int t = linear - b * g.tiles_per_batch;
   if (g.sym) {
@@ -114,7 +114,8 @@ __device__ __forceinline__ void decode_tile(const GemmGeom& g, int linear, int& 
     const int per_group = group * g.tiles_n;
     const int grp = t / per_group;
     const int in_group = t - grp * per_group;
-    const int rows = min(group, g.tiles_m - grp * group);
+    const int left = g.tiles_m - grp * group;
+    const int rows = left < group ? left : group;
     tn = in_group / rows;
     tm = grp * group + (in_group - tn * rows);
   }

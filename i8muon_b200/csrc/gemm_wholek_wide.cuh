@@ -43,18 +43,19 @@ __host__ __device__ inline int wide_units_per_batch(int tiles_m, int tiles_n, in
 // blocks 0..i of the right operand, a cyclic pattern that an LRU cache larger than L2 never hits.)
 // In a symmetric product a group of rows r0 .. r0 + R - 1 has r0 / 2 + 1 full columns of units and
 // then columns of R - 2, R - 4, ... units (rows tm >= 2 tw only).
-__device__ __forceinline__ void decode_unit(const GemmGeom& g, int units_per_batch, int linear, int& b, int& tm,
-                                            int& tn, int& width) {
+__host__ __device__ __forceinline__ void decode_unit(const GemmGeom& g, int units_per_batch, int linear, int& b,
+                                                     int& tm, int& tn, int& width) {
   b = linear / units_per_batch;
   int u = linear - b * units_per_batch;
   const int group = g.group;   // even, >= 2
   if (g.sym) {
     // the group that holds u: groups are whole rows, so the row search of the triangle finds it
-    int i = min(g.tiles_m - 1, int(2.f * sqrtf(float(u))));
+    int i = int(2.f * sqrtf(float(u)));
+    if (i > g.tiles_m - 1) i = g.tiles_m - 1;
     while (i + 1 < g.tiles_m && wide_units_before_row(i + 1) <= u) ++i;
     while (i > 0 && wide_units_before_row(i) > u) --i;
     const int r0 = i / group * group;
-    const int rows = min(group, g.tiles_m - r0);
+    const int rows = g.tiles_m - r0 < group ? g.tiles_m - r0 : group;
     u -= wide_units_before_row(r0);
     const int full = r0 / 2 + 1;
     int tw;
@@ -75,7 +76,7 @@ __device__ __forceinline__ void decode_unit(const GemmGeom& g, int units_per_bat
     const int per_group = group * cols;
     const int grp = u / per_group;
     const int in_group = u - grp * per_group;
-    const int rows = min(group, g.tiles_m - grp * group);
+    const int rows = g.tiles_m - grp * group < group ? g.tiles_m - grp * group : group;
     const int tw = in_group / rows;
     tm = grp * group + (in_group - tw * rows);
     tn = 2 * tw;
