@@ -340,16 +340,12 @@ def run_other_config(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    host_issue = {}
-
     def timed(fn, count):
         barrier()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        began = time.perf_counter()
         for _ in range(count):
             fn()
-        host_issue["ms_per_step"] = (time.perf_counter() - began) / count * 1e3   # host time to queue a step
         end.record()
         barrier()
         ms = torch.tensor([start.elapsed_time(end)], device=dev)
